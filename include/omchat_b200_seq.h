@@ -26,6 +26,8 @@ extern "C" {
 #define OMC_ACT_NONE 0
 #define OMC_ACT_RELU2 1     /* max(z, 0)^2 */
 #define OMC_ACT_GELU_TANH 2 /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
+#define OMC_ACT_GELU_ERF 3  /* 0.5 z (1 + erf(z / sqrt 2)) */
+#define OMC_ACT_CLAMP_SWISH 4 /* omc_glu_mul only: a clamped gate times a clamped, shifted second half */
 
 /* Y[b][M,N] = act(alpha * X[b][M,K] W[b][N,K]^T) for b < batch, any M, N, K >= 1 (edges are bounds-checked).
  * x_dt / w_dt / y_dt: dtype codes; allowed (x, w): (f32, f32), (f32, bf16), (bf16, bf16). sx / sw / sy: element offsets
@@ -97,12 +99,13 @@ int omc_latent_decode_items(const int32_t* pos, const int32_t* slot, int B, int 
                             void* stream);
 
 /* Router with score correction and identity experts. z fp32 [T, ldz]: logits of E_tot = experts + identity outputs, and, when
- * has_gate, one more column: the shared expert's gate logit. s = softmax(z[:E_tot]); choice = s + correction (fp32 [E_tot] or
- * NULL); the `top` largest choices (ties: lowest index) -> ids int32 [T, top], weights = s of the chosen, not renormalised
- * -> w fp32 [T, top]; gate[t] = sigmoid(z[t, E_tot]); counts[e] += 1 for every chosen e < experts (identity experts - the
+ * has_gate, one more column: the shared expert's gate logit. s = softmax(z[:E_tot] + bias) (bias fp32 [E_tot] or NULL);
+ * choice = s + correction (fp32 [E_tot] or NULL); the `top` largest choices (ties: lowest index) -> ids int32 [T, top];
+ * weights = s of the chosen -> w fp32 [T, top], as they are (renorm 0) or divided by their sum (renorm 1: the softmax over the
+ * chosen logits alone); gate[t] = sigmoid(z[t, E_tot]); counts[e] += 1 for every chosen e < experts (identity experts - the
  * last E_tot - experts outputs - take no rows). E_tot <= 4096, top <= 32. */
-int omc_router_topk(const float* z, long long ldz, int T, int E_tot, int experts, int top, const float* correction, int has_gate,
-                    int32_t* ids, float* w, float* gate, int32_t* counts, void* stream);
+int omc_router_topk(const float* z, long long ldz, int T, int E_tot, int experts, int top, const float* correction,
+                    const float* bias, int renorm, int has_gate, int32_t* ids, float* w, float* gate, int32_t* counts, void* stream);
 
 /* Expert-sorted layout. plan: seg_start[e] = first row of expert e's segment, segments padded to whole `tile`-row tiles;
  * tile_group[i] = expert of tile i or -1 (max_tiles entries are written); counts and cursor are left zeroed for the next call.
@@ -120,10 +123,11 @@ int omc_moe_plan_scatter_small(int32_t* counts, int experts, int tile, int max_t
 
 /* Combine + output-side norm + residual in one pass over the row:
  * y = sum_j w[t,j] * (slot_of[t,j] >= 0 ? ys[slot_of[t,j]] : h32[t]) + gate[t] * ysh[t]   (ysh / gate may be NULL)
- * h32[t] += y / sqrt(mean(y^2) + eps) * (1 + nw);  xb[t] = round(h32[t]) (NULL to skip). ys / ysh fp32. */
+ * h32[t] += y / sqrt(mean(y^2) + eps) * (1 + nw);  xb[t] = round(h32[t]), or with w_next != NULL the next sublayer's normed input
+ * h32[t] / rms(h32[t]) * (1 + w_next) (xb NULL to skip). ys / ysh fp32; nw and w_next of nw_dt. */
 int omc_moe_combine_norm(const float* ys, long long ldys, const int32_t* slot_of, const float* w, int top, const float* gate,
                          const float* ysh, long long ldysh, const void* nw, int nw_dt, float eps, float* h32, long long ldh,
-                         void* xb, int xb_dt, long long ldxb, int T, int C, void* stream);
+                         const void* w_next, void* xb, int xb_dt, long long ldxb, int T, int C, void* stream);
 
 /* omc_linear with a bias row: Y = act(alpha * X W^T + bias). bias [N] has the weights' dtype; batch item b reads bias + b * sbias.
  * NULL bias: omc_linear. Not with a tile table. */
@@ -141,8 +145,17 @@ int omc_post_norm_residual(const float* y1, long long ld1, const void* wa, const
                            const void* w_post, int w_dt, float eps, float mult, float* h32, long long ldh, const void* w_next,
                            void* xb, int xb_dt, long long ldxb, int rows, int C, void* stream);
 
-/* y[t, c] = act(z[t, c]) * z[t, n + c] for c < n: the two halves of a stacked gate | up projection. z of z_dt, fp32 arithmetic. */
-int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int n, int act, void* y, int y_dt, long long ldy, void* stream);
+/* y[t, c] = act(z[t, c]) * z[t, n + c] for c < n: the two halves of a stacked gate | up projection. z of z_dt, fp32 arithmetic.
+ * act OMC_ACT_CLAMP_SWISH: g = min(z[t, c], limit), u = clamp(z[t, n + c], -limit, limit), y = g * sigmoid(slope * g) * (u + shift);
+ * limit, slope and shift are ignored by the other activations. */
+int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int n, int act, float limit, float slope, float shift, void* y,
+                int y_dt, long long ldy, void* stream);
+
+/* h32[t, :] = table[ids[t], :] * scale + s(pos[t]) with the sinusoidal position vector s(p)[2i] = sin(p * freq[i]),
+ * s(p)[2i + 1] = cos(p * freq[i]); freq is a device table of ceil(C / 2) doubles (the angle is formed and reduced in double precision).
+ * ids outside [0, vocab) contribute no embedding row. */
+int omc_embed_sinusoid(const int32_t* ids, const int32_t* pos, int T, const void* table, int t_dt, int C, int vocab, float scale,
+                       const double* freq, float* h32, long long ldh, void* stream);
 
 /* Causal convolution over time per channel, then silu, then optional unit vectors. Row t is position pos[t] of the request in
  * state slot slot[t]; rows of one request are consecutive and ascending. w [ch, taps] of w_dt: the last tap multiplies the row
@@ -154,6 +167,13 @@ int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int n, int act
 int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps, const int32_t* pos,
                          const int32_t* slot, float* state, float* y, long long ldy, int unit_channels, int unit_group,
                          float unit_eps, int scaled_channels, float unit_mult, int single_rows, void* stream);
+
+/* The same convolution with the activation as a parameter: act OMC_CONV_LINEAR (the weighted sum itself) or OMC_CONV_SILU. */
+#define OMC_CONV_LINEAR 0
+#define OMC_CONV_SILU 1
+int omc_causal_conv(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps, const int32_t* pos,
+                    const int32_t* slot, float* state, float* y, long long ldy, int act, int unit_channels, int unit_group,
+                    float unit_eps, int scaled_channels, float unit_mult, int single_rows, void* stream);
 
 /* Linear-state recurrence per head with an fp32 state S [dim, vdim] in state[slot][head]:
  *   S <- diag(g_t) S;  u_t = beta_t (v_t - S^T k_t) (beta != NULL) or v_t;  S <- S + k_t u_t^T;  o_t = S^T q_t.
@@ -173,29 +193,40 @@ int omc_linear_state_scan(const float* q, long long ldq, const float* k, long lo
 int omc_gated_rms_rows(const float* x, long long ldx, int rows, int groups, int n, const void* w, int w_dt, float eps,
                        const float* gate, long long ldg, int gate_act, void* y, int y_dt, long long ldy, void* stream);
 
-/* Rows of a step for windowed attention: q_out[t] = q[t, :nq] / rms * wq (plain weight, over all query columns at once); the
- * cache row of (slot[t], pos[t]) <- [k[t, :nk] / rms * wk | v[t, :nv]]. Pool [pages][page_size][nk + nv] and q_out of dtype dt. */
-int omc_qk_norm_kv_store(const float* q, long long ldq, int nq, const void* wq, const float* k, long long ldk, int nk, const void* wk,
-                         int w_dt, const float* v, long long ldv, int nv, float eps, int T, const int32_t* pos, const int32_t* slot,
-                         const int32_t* block_table, int max_pages, int page_size, void* pool, void* q_out, long long ldqo, int dt,
-                         void* stream);
+/* Rows of a step for windowed attention: q_out[t] = q[t, :nq] / rms * wq (plain weight); the cache row of (slot[t], pos[t]) <-
+ * [k[t, :nk] / rms * wk | v[t, :nv]]. q_group / k_group 0: one norm over all nq (nk) columns at once, weight [nq] ([nk]); > 0: one norm
+ * per that many consecutive columns (a head, or one score map of a head) with a weight of that size shared by the groups.
+ * Pool [pages][page_size][nk + nv] and q_out of dtype dt. */
+int omc_qk_norm_kv_store(const float* q, long long ldq, int nq, int q_group, const void* wq, const float* k, long long ldk, int nk,
+                         int k_group, const void* wk, int w_dt, const float* v, long long ldv, int nv, float eps, int T,
+                         const int32_t* pos, const int32_t* slot, const int32_t* block_table, int max_pages, int page_size, void* pool,
+                         void* q_out, long long ldqo, int dt, void* stream);
 
-/* Sliding-window attention over such a pool: row t (position p of its slot) sees the keys j with 0 <= p - j < window.
- * score = (q_h . k_j) * scale; softcap > 0: score = softcap * tanh(score / softcap); dist_bias != NULL (fp32 [window, H]):
- * score += dist_bias[p - j][h]; softmax; out[t, h * dv + :] = sum_j p_j v_j. Query head h reads key/value head h / (H / G).
- * q [T, >= H * d] and pool of dtype dt, out of out_dt. dv <= 256. */
-int omc_window_attn(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool, int dt,
+/* Sliding-window attention over such a pool: row t (position p of its slot) sees the keys j <= p with p - j < window or
+ * j < keep_first (the first keys of the sequence stay visible; 0: none). score = (q . k) * scale; softcap > 0: score = softcap *
+ * tanh(score / softcap); dist_bias != NULL (fp32 [window, H]): score += dist_bias[p - j][h] for p - j < window; softmax;
+ * out = sum_j p_j v_j. Query head h reads key/value head h / (H / G). maps >= 1 score maps per head: q is [T, H, maps, d], a cache
+ * row [G, maps, d keys | G, dv values], out [T, H, maps, dv] - every map is a softmax of its own over the same values.
+ * q and pool of dtype dt, out of out_dt. dv <= 256. */
+int omc_window_attn(const void* q, long long ldq, int T, int H, int G, int d, int dv, int maps, const void* pool, int dt,
                     const int32_t* block_table, int max_pages, int page_size, const int32_t* pos, const int32_t* slot, int window,
-                    float scale, float softcap, const float* dist_bias, void* out, int out_dt, long long ldo, void* stream);
+                    int keep_first, float scale, float softcap, const float* dist_bias, void* out, int out_dt, long long ldo, void* stream);
 
 /* Tensor-core version of omc_window_attn (bf16 q and pool; d and dv multiples of 16, d <= 256, dv <= 128, H / G a divisor of 64 -
  * omc_window_attn_mma_ok says 1). items: int32 [n_items][4] (first_row, n_tok, slot, first_pos), n_tok <= 64 / (H / G) consecutive
  * rows of one request; items NULL: every one of the T rows is an item of its own, taken from pos / slot on the device. Same
  * results as omc_window_attn up to the bf16 rounding of the probabilities and the hardware tanh of the soft cap. */
 int omc_window_attn_mma_ok(int H, int G, int d, int dv);
-int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool, const int32_t* block_table,
-                        int max_pages, int page_size, const int32_t* items, int n_items, const int32_t* pos, const int32_t* slot,
-                        int window, float scale, float softcap, const float* dist_bias, void* out, int out_dt, long long ldo, void* stream);
+int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d, int dv, int maps, const void* pool,
+                        const int32_t* block_table, int max_pages, int page_size, const int32_t* items, int n_items, const int32_t* pos,
+                        const int32_t* slot, int window, int keep_first, float scale, float softcap, const float* dist_bias, void* out,
+                        int out_dt, long long ldo, void* stream);
+
+/* Differential heads: a fp32 [T, H, 2, dv] (two score maps per head) -> o = a1 - lambda * a2; o / sqrt(mean(o^2) + eps) over the
+ * head's dv values; times mult; times act(gate[t, h * dv + c]) (gate fp32 or NULL; gate_act 0: as is, 1: silu, 2: sigmoid)
+ * -> y [T, H * dv] of y_dt. */
+int omc_diff_heads_gate(const float* a, long long lda, int T, int H, int dv, float lambda, float mult, float eps, const float* gate,
+                        long long ldg, int gate_act, void* y, int y_dt, long long ldy, void* stream);
 
 /* In place over x[t, :cols] (fp32): op 1: silu; op 2: x <- exp(-exp(A_log[c / group]) * softplus(x + bias[c])) - the same
  * functions the recurrence applies while staging, as one pass for steps with long portions. */

@@ -424,3 +424,132 @@ class TifisunConfig:
                 "embedding": {"scale": self.embedding_scale}, "residual_mult": self.residual_mult, "norm": {"eps": self.norm_eps},
                 "layers": out, "kv_page_size": self.kv_page_size, "eos_token_id": self.eos_token_id,
                 "pad_token_id": self.pad_token_id}
+
+
+# --------------------------------------------------------------------------------------------------------------------- Fofisun
+@dataclass
+class DiffAttentionSpec:
+    """Differential softmax attention without rotation: every head has two score maps (queries and keys of their own, `dim` wide)
+    over one set of values; o = a1 - lambda a2, RMS-normed over the head and scaled by 1 - diff, lambda = exp(lq1 . lk1) -
+    exp(lq2 . lk2) + diff. conv: taps of the causal per-channel convolution behind the q, k, v projections (0: none). Queries and
+    keys are RMS-normed per head and map. window: keys a row sees behind itself, itself included (None: all); keep_first: the
+    first keys of the sequence stay visible behind the window. The concatenated heads pass a sigmoid gate."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    diff: float
+    window: Optional[int] = None
+    keep_first: int = 0
+    conv: int = 0
+
+
+@dataclass
+class GeluMlpSpec:
+    """W_down gelu(W_up x) with the erf form of gelu, no biases."""
+    ff: int
+
+
+@dataclass
+class ClampedMoeSpec:
+    """`experts` gated experts of width expert_ff, `top` per token chosen by the router's logits (weights: softmax over the chosen
+    logits alone). An expert: g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit), W_down (g sigmoid(1.702 g) (u + 1)).
+    shared_ff: width of an expert that every token passes, scaled by a sigmoid gate of the token (None: none)."""
+    experts: int
+    top: int
+    expert_ff: int
+    limit: float
+    shared_ff: Optional[int] = None
+    shared_limit: float = 0.0
+
+
+@dataclass
+class FofisunLayerSpec:
+    type: str                      # 'attention'
+    mixer: DiffAttentionSpec
+    mlp: object                    # GeluMlpSpec | ClampedMoeSpec | None
+
+
+@dataclass
+class FofisunConfig:
+    model_type: str = "fofisun"
+    vocab_size: int = 0
+    hidden_size: int = 0
+    norm_eps: float = 1e-6
+    layers: List[FofisunLayerSpec] = field(default_factory=list)
+    loop_start: int = 0            # layers loop_start .. loop_stop - 1 run loop_times times in a row (the same tensors, a cache per run)
+    loop_stop: int = 0
+    loop_times: int = 1
+    kv_page_size: int = 64         # engine knob: tokens per cache page
+    eos_token_id: int = -1
+    pad_token_id: int = 0
+
+    MIXERS = ("attention",)
+    POSITION_BASE = 10000.0        # sinusoidal position vectors: entry 2i / 2i + 1 = sin / cos(p * base^(-2i / width))
+    SWISH_SLOPE = 1.702            # the experts' gate is g * sigmoid(SWISH_SLOPE * g)
+    UP_SHIFT = 1.0                 # ... times (u + UP_SHIFT)
+
+    def layer_runs(self) -> List[int]:
+        """The layer index of every layer run, in execution order."""
+        n = len(self.layers)
+        if self.loop_stop <= self.loop_start:
+            return list(range(n))
+        return list(range(self.loop_start)) + list(range(self.loop_start, self.loop_stop)) * self.loop_times + list(range(self.loop_stop, n))
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "FofisunConfig":
+        layers = []
+        for i, ld in enumerate(d["layers"]):
+            typ, m = ld["type"], ld["mixer"]
+            if typ not in cls.MIXERS:
+                raise ValueError(f"layer {i}: unknown mixer type {typ!r}")
+            mask = m.get("mask") or {}
+            mix = DiffAttentionSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                    scale=float(m["scale"]), diff=float(m["diff"]),
+                                    window=int(mask["size"]) if mask.get("size") is not None else None,
+                                    keep_first=int(mask.get("keep_first") or 0), conv=int(m.get("conv") or 0))
+            if mix.heads < 1 or mix.kv_heads < 1 or mix.heads % mix.kv_heads or mix.conv < 0 or mix.keep_first < 0 or \
+                    (mix.window is not None and mix.window < 1):
+                raise ValueError(f"layer {i}: inconsistent mixer sizes")
+            md, mlp = ld.get("mlp"), None
+            if md:
+                kind = md.get("kind", "dense")
+                if kind == "dense":
+                    mlp = GeluMlpSpec(ff=int(md["ff"]))
+                elif kind == "moe":
+                    r, e, sh = md["router"], md["expert"], md.get("shared")
+                    mlp = ClampedMoeSpec(experts=int(r["experts"]), top=int(r["top"]), expert_ff=int(e["ff"]), limit=float(e["limit"]),
+                                         shared_ff=int(sh["ff"]) if sh else None, shared_limit=float(sh["limit"]) if sh else 0.0)
+                    if not 1 <= mlp.top <= mlp.experts:
+                        raise ValueError(f"layer {i}: top must be between 1 and the number of experts")
+                else:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
+            layers.append(FofisunLayerSpec(type=typ, mixer=mix, mlp=mlp))
+        lp = d.get("loop") or {}
+        start, stop, times = int(lp.get("start", 0)), int(lp.get("stop", 0)), int(lp.get("times", 1))
+        if lp and not (0 <= start <= stop <= len(layers) and times >= 1):
+            raise ValueError("loop: start <= stop within the layers and times >= 1 are required")
+        return cls(vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)),
+                   layers=layers, loop_start=start, loop_stop=stop, loop_times=times, kv_page_size=int(d.get("kv_page_size", 64)),
+                   eos_token_id=int(d.get("eos_token_id", -1)), pad_token_id=int(d.get("pad_token_id", 0)))
+
+    def to_dict(self) -> dict:
+        """The config.json form (round-trips through from_dict)."""
+        out = []
+        for l in self.layers:
+            m = l.mixer
+            md = {"conv": m.conv, "diff": m.diff, "dim": m.dim, "heads": m.heads, "kv_heads": m.kv_heads,
+                  "mask": {"keep_first": m.keep_first, "size": m.window}, "scale": m.scale, "vdim": m.vdim}
+            if isinstance(l.mlp, GeluMlpSpec):
+                mlp = {"ff": l.mlp.ff, "kind": "dense"}
+            elif isinstance(l.mlp, ClampedMoeSpec):
+                s = l.mlp
+                mlp = {"expert": {"ff": s.expert_ff, "limit": s.limit}, "kind": "moe", "router": {"experts": s.experts, "top": s.top},
+                       "shared": {"ff": s.shared_ff, "limit": s.shared_limit} if s.shared_ff else None}
+            else:
+                mlp = None
+            out.append({"type": l.type, "mixer": md, "mlp": mlp})
+        return {"architecture": "Fofisun", "vocab": self.vocab_size, "width": self.hidden_size, "norm": {"eps": self.norm_eps},
+                "layers": out, "loop": {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times},
+                "kv_page_size": self.kv_page_size, "eos_token_id": self.eos_token_id, "pad_token_id": self.pad_token_id}

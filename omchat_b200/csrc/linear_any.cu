@@ -31,6 +31,7 @@ __device__ __forceinline__ float apply_act(float z, int act) {
     return z * z;
   }
   if (act == OMC_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (act == OMC_ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
   return z;
 }
 

@@ -1,8 +1,9 @@
 // Mixture-of-experts routing with a score correction and identity experts, the expert-sorted row layout, and the combine that is
 // fused with the output-side norm and the residual add.
 //
-//   router:   s = softmax(z) over ALL router outputs (experts, then identity experts); the choice is made on s + correction, the
-//             mixing weights are the uncorrected s of the chosen outputs (not renormalised). An identity expert returns its input,
+//   router:   s = softmax(z + bias) over ALL router outputs (experts, then identity experts); the choice is made on s + correction, the
+//             mixing weights are the uncorrected s of the chosen outputs - as they are, or divided by their sum (`renorm`), which is
+//             the softmax over the chosen logits alone. An identity expert returns its input,
 //             has no weights and takes no rows in the sorted layout. The shared expert's gate logit rides as one more column of z.
 //   plan:     one CTA: segment starts padded to whole row tiles, tile -> expert table, counters reset for the next call.
 //   scatter:  one CTA per row: the row is copied to a place in the segment of each chosen expert (atomic cursor per expert; the
@@ -19,6 +20,7 @@ constexpr int kRouteWarps = 4;
 // One warp per row. Shared memory per warp: s[E_tot] (softmax scores) and ch[E_tot] (choice values, -inf once taken).
 __global__ void __launch_bounds__(kRouteWarps * 32) router_topk_kernel(const float* __restrict__ z, long long ldz, int T, int E_tot,
                                                                        int experts, int top, const float* __restrict__ correction,
+                                                                       const float* __restrict__ bias, int renorm,
                                                                        int has_gate, int32_t* __restrict__ ids, float* __restrict__ w,
                                                                        float* __restrict__ gate, int32_t* __restrict__ counts) {
   extern __shared__ float sm[];
@@ -29,11 +31,15 @@ __global__ void __launch_bounds__(kRouteWarps * 32) router_topk_kernel(const flo
   float* ch = s + E_tot;
   const float* zr = z + (long long)t * ldz;
   float mx = -INFINITY;
-  for (int e = lane; e < E_tot; e += 32) mx = fmaxf(mx, zr[e]);
+  for (int e = lane; e < E_tot; e += 32) {
+    const float v = bias != nullptr ? zr[e] + bias[e] : zr[e];
+    ch[e] = v;   // the logit with its bias; replaced by the choice value below
+    mx = fmaxf(mx, v);
+  }
   mx = seq_warp_max(mx);
   float sum = 0.f;
   for (int e = lane; e < E_tot; e += 32) {
-    const float p = expf(zr[e] - mx);
+    const float p = expf(ch[e] - mx);
     s[e] = p;
     sum += p;
   }
@@ -42,7 +48,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) router_topk_kernel(const flo
   for (int e = lane; e < E_tot; e += 32) {
     const float p = s[e] * inv;
     s[e] = p;
-    ch[e] = correction != nullptr ? p + correction[e] : p;
+    if (correction != nullptr) ch[e] = p + correction[e];   // without a correction the choice is made on the logits themselves
   }
   __syncwarp();
   for (int k = 0; k < top; ++k) {
@@ -72,6 +78,12 @@ __global__ void __launch_bounds__(kRouteWarps * 32) router_topk_kernel(const flo
       ch[be] = -INFINITY;
     }
     __syncwarp();
+  }
+  if (renorm && lane == 0) {   // softmax over the chosen alone: exp(z - max) / sum over the chosen, the common factor cancels
+    float tot = 0.f;
+    for (int k = 0; k < top; ++k) tot += w[(long long)t * top + k];
+    const float r = 1.f / tot;
+    for (int k = 0; k < top; ++k) w[(long long)t * top + k] *= r;
   }
   if (has_gate && lane == 0) gate[t] = 1.f / (1.f + expf(-zr[E_tot]));
 }
@@ -169,8 +181,8 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const float* __re
                                                                const int32_t* __restrict__ slot_of, const float* __restrict__ w, int top,
                                                                const float* __restrict__ gate, const float* __restrict__ ysh,
                                                                long long ldysh, const TW* __restrict__ nw, float eps,
-                                                               float* __restrict__ h32, long long ldh, TB* __restrict__ xb,
-                                                               long long ldxb, int C) {
+                                                               float* __restrict__ h32, long long ldh, const TW* __restrict__ w_next,
+                                                               TB* __restrict__ xb, long long ldxb, int C) {
   extern __shared__ float srow[];  // y [C]
   __shared__ float red[33];
   __shared__ int s_slot[32];
@@ -196,11 +208,18 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const float* __re
   }
   ss = block_sum(ss, red);
   const float rstd = 1.f / sqrtf(ss / (float)C + eps);
+  float sh = 0.f;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     const float v = hr[c] + srow[c] * rstd * (1.f + ldf(nw + c));
     hr[c] = v;
-    if (xb != nullptr) stf(xb + (long long)t * ldxb + c, v);
+    srow[c] = v;
+    sh = fmaf(v, v, sh);
+    if (xb != nullptr && w_next == nullptr) stf(xb + (long long)t * ldxb + c, v);
   }
+  if (xb == nullptr || w_next == nullptr) return;
+  sh = block_sum(sh, red);   // the next sublayer reads the row normed: x / rms(x) * (1 + w_next)
+  const float rn = 1.f / sqrtf(sh / (float)C + eps);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) stf(xb + (long long)t * ldxb + c, srow[c] * rn * (1.f + ldf(w_next + c)));
 }
 
 }  // namespace omc
@@ -208,7 +227,8 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const float* __re
 using namespace omc;
 
 extern "C" int omc_router_topk(const float* z, long long ldz, int T, int E_tot, int experts, int top, const float* correction,
-                               int has_gate, int32_t* ids, float* w, float* gate, int32_t* counts, void* stream) {
+                               const float* bias, int renorm, int has_gate, int32_t* ids, float* w, float* gate, int32_t* counts,
+                               void* stream) {
   if (z == nullptr || ids == nullptr || w == nullptr || counts == nullptr || T < 0 || E_tot <= 0 || experts < 0 || experts > E_tot ||
       top <= 0 || top > E_tot || (has_gate && gate == nullptr))
     return set_error(OMC_ERR_ARG, "omc_router_topk: bad argument");
@@ -220,7 +240,7 @@ extern "C" int omc_router_topk(const float* z, long long ldz, int T, int E_tot, 
     if (e != cudaSuccess) return set_error(OMC_ERR_CUDA, cudaGetErrorString(e));
   }
   router_topk_kernel<<<(T + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
-      z, ldz, T, E_tot, experts, top, correction, has_gate, ids, w, gate, counts);
+      z, ldz, T, E_tot, experts, top, correction, bias, renorm, has_gate, ids, w, gate, counts);
   return check_launch("omc_router_topk");
 }
 
@@ -263,7 +283,7 @@ extern "C" int omc_moe_plan_scatter_small(int32_t* counts, int experts, int tile
 
 extern "C" int omc_moe_combine_norm(const float* ys, long long ldys, const int32_t* slot_of, const float* w, int top, const float* gate,
                                     const float* ysh, long long ldysh, const void* nw, int nw_dt, float eps, float* h32, long long ldh,
-                                    void* xb, int xb_dt, long long ldxb, int T, int C, void* stream) {
+                                    const void* w_next, void* xb, int xb_dt, long long ldxb, int T, int C, void* stream) {
   if (slot_of == nullptr || w == nullptr || nw == nullptr || h32 == nullptr || T < 0 || C <= 0 || top <= 0 || top > 32)
     return set_error(OMC_ERR_ARG, "omc_moe_combine_norm: bad argument");
   if (T == 0) return OMC_OK;
@@ -276,7 +296,7 @@ extern "C" int omc_moe_combine_norm(const float* ys, long long ldys, const int32
       if (e != cudaSuccess) return set_error(OMC_ERR_CUDA, cudaGetErrorString(e));
     }
     moe_combine_norm_kernel<TW, TB><<<T, 256, smem, st>>>(ys, ldys, slot_of, w, top, gate, ysh, ldysh, static_cast<const TW*>(nw), eps,
-                                                          h32, ldh, static_cast<TB*>(xb), ldxb, C);
+                                                          h32, ldh, static_cast<const TW*>(w_next), static_cast<TB*>(xb), ldxb, C);
   }))
   return check_launch("omc_moe_combine_norm");
 }

@@ -19,6 +19,25 @@ __global__ void __launch_bounds__(256) embed_scale_kernel(const int32_t* __restr
   }
 }
 
+// Embedding row plus the sinusoidal position vector: entry 2i is sin(p * f_i), entry 2i + 1 is cos(p * f_i). The angle is formed
+// and reduced in double precision (f_i arrives as a double table), so it is exact to fp32 at any position.
+template <typename TT>
+__global__ void __launch_bounds__(256) embed_sinusoid_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ pos,
+                                                             const TT* __restrict__ table, int C, int vocab, float scale,
+                                                             const double* __restrict__ freq, float* __restrict__ h32, long long ldh) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  const double p = (double)pos[t];
+  for (int i = threadIdx.x; 2 * i < C; i += blockDim.x) {
+    double sn, cs;
+    sincos(p * freq[i], &sn, &cs);
+    const int c = 2 * i;
+    h32[(long long)t * ldh + c] = (ok ? ldf(table + (long long)id * C + c) * scale : 0.f) + (float)sn;
+    if (c + 1 < C) h32[(long long)t * ldh + c + 1] = (ok ? ldf(table + (long long)id * C + c + 1) * scale : 0.f) + (float)cs;
+  }
+}
+
 template <typename TW, typename TY>
 __global__ void __launch_bounds__(256) rms_rows_kernel(const float* __restrict__ x, long long ldx, const TW* __restrict__ w,
                                                        int one_plus, float eps, TY* __restrict__ y, long long ldy, int n) {
@@ -133,14 +152,24 @@ __device__ __forceinline__ void st4(bf16_t* p, const float (&v)[4]) {
   *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(v[2], v[3]);
   *reinterpret_cast<uint2*>(p) = t;
 }
-__device__ __forceinline__ float glu_act(float g, int act) {
-  if (act == OMC_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-  if (act == OMC_ACT_RELU2) return fmaxf(g, 0.f) * fmaxf(g, 0.f);
-  return g;
+struct GluParams {
+  int act;
+  float limit, slope, shift;   // OMC_ACT_CLAMP_SWISH only
+};
+__device__ __forceinline__ float glu_pair(float g, float u, const GluParams& p) {
+  if (p.act == OMC_ACT_CLAMP_SWISH) {
+    g = fminf(g, p.limit);
+    u = fminf(fmaxf(u, -p.limit), p.limit);
+    return g / (1.f + expf(-p.slope * g)) * (u + p.shift);
+  }
+  if (p.act == OMC_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  if (p.act == OMC_ACT_GELU_ERF) return 0.5f * g * (1.f + erff(g * 0.70710678118654752f)) * u;
+  if (p.act == OMC_ACT_RELU2) return fmaxf(g, 0.f) * fmaxf(g, 0.f) * u;
+  return g * u;
 }
 
 template <typename TZ, typename TY, int VEC>
-__global__ void __launch_bounds__(256) glu_mul_kernel(const TZ* __restrict__ z, long long ldz, int n, int act, TY* __restrict__ y,
+__global__ void __launch_bounds__(256) glu_mul_kernel(const TZ* __restrict__ z, long long ldz, int n, GluParams gp, TY* __restrict__ y,
                                                       long long ldy, long long total) {
   const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per VEC columns
   if (e >= total) return;
@@ -152,10 +181,10 @@ __global__ void __launch_bounds__(256) glu_mul_kernel(const TZ* __restrict__ z, 
     ld4(z + t * ldz + c, g);
     ld4(z + t * ldz + n + c, u);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) g[i] = glu_act(g[i], act) * u[i];
+    for (int i = 0; i < 4; ++i) g[i] = glu_pair(g[i], u[i], gp);
     st4(y + t * ldy + c, g);
   } else {
-    stf(y + t * ldy + c, glu_act(ldf(z + t * ldz + c), act) * ldf(z + t * ldz + n + c));
+    stf(y + t * ldy + c, glu_pair(ldf(z + t * ldz + c), ldf(z + t * ldz + n + c), gp));
   }
 }
 
@@ -215,15 +244,29 @@ extern "C" int omc_post_norm_residual(const float* y1, long long ld1, const void
   return check_launch("omc_post_norm_residual");
 }
 
-extern "C" int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int n, int act, void* y, int y_dt, long long ldy, void* stream) {
+extern "C" int omc_glu_mul(const void* z, int z_dt, long long ldz, int rows, int n, int act, float limit, float slope, float shift,
+                           void* y, int y_dt, long long ldy, void* stream) {
   if (z == nullptr || y == nullptr || rows < 0 || n <= 0) return set_error(OMC_ERR_ARG, "omc_glu_mul: bad argument");
   if (rows == 0) return OMC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long total = (long long)rows * n;
   const bool vec = n % 4 == 0 && ldz % 4 == 0 && ldy % 4 == 0 && reinterpret_cast<uintptr_t>(z) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
+  const GluParams gp{act, limit, slope, shift};
   OMC_DT_SWITCH(z_dt, TZ, OMC_DT_SWITCH(y_dt, TY, {
-    if (vec) glu_mul_kernel<TZ, TY, 4><<<(unsigned)((total / 4 + 255) / 256), 256, 0, st>>>(static_cast<const TZ*>(z), ldz, n, act, static_cast<TY*>(y), ldy, total / 4);
-    else glu_mul_kernel<TZ, TY, 1><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const TZ*>(z), ldz, n, act, static_cast<TY*>(y), ldy, total);
+    if (vec) glu_mul_kernel<TZ, TY, 4><<<(unsigned)((total / 4 + 255) / 256), 256, 0, st>>>(static_cast<const TZ*>(z), ldz, n, gp, static_cast<TY*>(y), ldy, total / 4);
+    else glu_mul_kernel<TZ, TY, 1><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const TZ*>(z), ldz, n, gp, static_cast<TY*>(y), ldy, total);
   }))
   return check_launch("omc_glu_mul");
+}
+
+extern "C" int omc_embed_sinusoid(const int32_t* ids, const int32_t* pos, int T, const void* table, int t_dt, int C, int vocab, float scale,
+                                  const double* freq, float* h32, long long ldh, void* stream) {
+  if (ids == nullptr || pos == nullptr || table == nullptr || freq == nullptr || h32 == nullptr || T < 0 || C <= 0)
+    return set_error(OMC_ERR_ARG, "omc_embed_sinusoid: bad argument");
+  if (T == 0) return OMC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OMC_DT_SWITCH(t_dt, TT, {
+    embed_sinusoid_kernel<TT><<<T, 256, 0, st>>>(ids, pos, static_cast<const TT*>(table), C, vocab, scale, freq, h32, ldh);
+  })
+  return check_launch("omc_embed_sinusoid");
 }

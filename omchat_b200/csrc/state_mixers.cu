@@ -22,7 +22,7 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
-// ---- causal convolution + silu (+ unit vectors) ---------------------------------------------------------------------------
+// ---- causal convolution (+ silu) (+ unit vectors) ---------------------------------------------------------------------------
 // One CTA per (1 or 8 consecutive rows, block of channels; blocks are whole unit-vector groups). Tap j of `taps` multiplies the input
 // `taps - 1 - j` positions back: an earlier row of the same step when that row belongs to the same request, else the state ring
 // state[slot][position % (taps - 1)][channel], else (before position 0) zero. save_here: every row of the step is a request of
@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __re
                                                                const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
                                                                float* __restrict__ state, float* __restrict__ y, long long ldy,
                                                                int unit_channels, int unit_group, float unit_eps, int scaled_channels,
-                                                               float unit_mult, int save_here) {
+                                                               float unit_mult, int save_here, int act) {
   extern __shared__ float tile[];  // [rows_per_cta][ch_block]
   __shared__ const float* src[kConvRows][kConvMaxTaps];   // where tap j of row r reads: a row of x, a ring entry, or nothing
   const int t0 = blockIdx.x * rows_per_cta, nr = min(rows_per_cta, T - t0);
@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __re
         const float xv = q != nullptr ? q[c] : 0.f;
         acc = fmaf(ldf(w + (long long)c * taps + j), xv, acc);
       }
-      tile[r * ch_block + cl] = silu_f(acc);
+      tile[r * ch_block + cl] = act ? silu_f(acc) : acc;
       // this thread is the only one that touches channel c of the ring: its write follows its reads
       if (save_here && R > 0) state[((long long)slot[t0 + r] * R + pos[t0 + r] % R) * ch + c] = x[(long long)(t0 + r) * ldx + c];
     }
@@ -375,12 +375,12 @@ __global__ void __launch_bounds__(256) gated_rms_kernel(const float* __restrict_
 
 using namespace omc;
 
-extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps,
-                                    const int32_t* pos, const int32_t* slot, float* state, float* y, long long ldy,
-                                    int unit_channels, int unit_group, float unit_eps, int scaled_channels, float unit_mult,
-                                    int single_rows, void* stream) {
+extern "C" int omc_causal_conv(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps,
+                               const int32_t* pos, const int32_t* slot, float* state, float* y, long long ldy, int act,
+                               int unit_channels, int unit_group, float unit_eps, int scaled_channels, float unit_mult,
+                               int single_rows, void* stream) {
   if (x == nullptr || w == nullptr || pos == nullptr || slot == nullptr || y == nullptr || T < 0 || ch <= 0 || taps < 1 || taps > kConvMaxTaps ||
-      (taps > 1 && state == nullptr) || unit_channels < 0 || unit_channels > ch || (unit_channels > 0 && (unit_group <= 0 || unit_channels % unit_group)) ||
+      (taps > 1 && state == nullptr) || (act != OMC_CONV_LINEAR && act != OMC_CONV_SILU) || unit_channels < 0 || unit_channels > ch || (unit_channels > 0 && (unit_group <= 0 || unit_channels % unit_group)) ||
       (unit_channels > 0 && scaled_channels % unit_group))
     return set_error(OMC_ERR_ARG, "omc_causal_conv_silu: bad argument");
   if (T == 0) return OMC_OK;
@@ -398,10 +398,18 @@ extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch
     if (smem > 48 * 1024) cudaFuncSetAttribute(causal_conv_silu_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     causal_conv_silu_kernel<TW><<<dim3((T + rows_per_cta - 1) / rows_per_cta, blocks), 256, smem, st>>>(x, ldx, T, ch, ch_block, rows_per_cta, static_cast<const TW*>(w), taps, pos, slot, state, y,
                                                                     ldy, unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
-                                                                    single_rows ? 1 : 0);
+                                                                    single_rows ? 1 : 0, act == OMC_CONV_SILU ? 1 : 0);
   })
   if (taps > 1 && !single_rows) conv_state_save_kernel<<<dim3(T, (ch + 1023) / 1024), 256, 0, st>>>(x, ldx, ch, taps - 1, T, pos, slot, state);
   return check_launch("omc_causal_conv_silu");
+}
+
+extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps,
+                                    const int32_t* pos, const int32_t* slot, float* state, float* y, long long ldy,
+                                    int unit_channels, int unit_group, float unit_eps, int scaled_channels, float unit_mult,
+                                    int single_rows, void* stream) {
+  return omc_causal_conv(x, ldx, T, ch, w, w_dt, taps, pos, slot, state, y, ldy, OMC_CONV_SILU, unit_channels, unit_group, unit_eps,
+                         scaled_channels, unit_mult, single_rows, stream);
 }
 
 extern "C" int omc_linear_state_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,

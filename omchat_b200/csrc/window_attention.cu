@@ -1,9 +1,13 @@
 // Sliding-window softmax attention over a paged key/value cache, without rotation: positions enter through a bias that depends on
 // the distance between query and key only. Per cached token one row [kv_heads * dim keys | kv_heads * vdim values].
 //
-//   omc_qk_norm_kv_store: the rows of a step -> normed queries, and normed keys + values appended to the pages
+//   omc_qk_norm_kv_store: the rows of a step -> normed queries, and normed keys + values appended to the pages (one RMS norm over the
+//                         whole projection, or one per group of columns - a head, or a score map of a head - with a shared weight)
 //   omc_window_attn:      score = (q . k) * scale -> softcap * tanh(score / softcap) -> + dist_bias[i - j][head] -> softmax over the
-//                         keys j with 0 <= i - j < window -> weighted sum of values
+//                         keys j with 0 <= i - j < window, and the first keep_first keys of the sequence whatever their distance
+//                         -> weighted sum of values. maps > 1: every head has that many score maps (queries and keys of their own)
+//                         over the same values; the maps come out side by side.
+//   omc_diff_heads_gate:  two maps -> o = a1 - lambda a2, RMS norm over the head, a constant factor, an elementwise gate
 // The distance bias arrives as a table [window, heads] that the host builds (here from a bucketed learned table; any function of
 // the distance fits). Prompt portions and decoded tokens are one case: row t at position pos[t] of slot[t] reads the cached
 // entries max(0, pos - window + 1) .. pos of its slot, which the store kernel of the same step has written.
@@ -17,11 +21,34 @@ namespace omc {
 constexpr int kWinWarps = 4;
 constexpr int kWinMaxPerLane = 8;  // value width up to 256
 
-// One CTA per row. q: RMS norm over all H * d query columns with a plain weight -> q_out. k likewise -> page; v copied -> page.
+// One CTA per row. q: RMS norm with a plain weight -> q_out; k likewise -> page; v copied -> page. group 0: one norm over all
+// columns, weight [n]; group > 0: one norm per `group` consecutive columns (a warp each), weight [group] shared by the groups.
+template <typename TW, typename TD>
+__device__ __forceinline__ void rms_to(const float* __restrict__ x, int n, int group, const TW* __restrict__ w, float eps,
+                                       TD* __restrict__ dst, float* red) {
+  if (group <= 0) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) ss = fmaf(x[c], x[c], ss);
+    ss = block_sum(ss, red);
+    const float rstd = 1.f / sqrtf(ss / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) stf(dst + c, x[c] * rstd * ldf(w + c));
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g * group < n; g += nw) {
+    const float* xg = x + g * group;
+    float ss = 0.f;
+    for (int c = lane; c < group; c += 32) ss = fmaf(xg[c], xg[c], ss);
+    ss = seq_warp_sum(ss);
+    const float rstd = 1.f / sqrtf(ss / (float)group + eps);
+    for (int c = lane; c < group; c += 32) stf(dst + g * group + c, xg[c] * rstd * ldf(w + c));
+  }
+}
+
 template <typename TW, typename TC>
-__global__ void __launch_bounds__(256) qk_norm_kv_store_kernel(const float* __restrict__ q, long long ldq, int nq,
+__global__ void __launch_bounds__(256) qk_norm_kv_store_kernel(const float* __restrict__ q, long long ldq, int nq, int q_group,
                                                                const TW* __restrict__ wq, const float* __restrict__ k, long long ldk,
-                                                               int nk, const TW* __restrict__ wk, const float* __restrict__ v,
+                                                               int nk, int k_group, const TW* __restrict__ wk, const float* __restrict__ v,
                                                                long long ldv, int nv, float eps, const int32_t* __restrict__ pos,
                                                                const int32_t* __restrict__ slot, const int32_t* __restrict__ block_table,
                                                                int max_pages, int page_size, TC* __restrict__ pool,
@@ -31,67 +58,58 @@ __global__ void __launch_bounds__(256) qk_norm_kv_store_kernel(const float* __re
   const int p = pos[t];
   const int page = block_table[(long long)slot[t] * max_pages + p / page_size];
   TC* dst = pool + ((long long)page * page_size + p % page_size) * (nk + nv);
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < nq; c += blockDim.x) {
-    const float x = q[t * ldq + c];
-    ss = fmaf(x, x, ss);
-  }
-  ss = block_sum(ss, red);
-  float rstd = 1.f / sqrtf(ss / (float)nq + eps);
-  for (int c = threadIdx.x; c < nq; c += blockDim.x) stf(q_out + t * ldqo + c, q[t * ldq + c] * rstd * ldf(wq + c));
-  ss = 0.f;
-  for (int c = threadIdx.x; c < nk; c += blockDim.x) {
-    const float x = k[t * ldk + c];
-    ss = fmaf(x, x, ss);
-  }
-  ss = block_sum(ss, red);
-  rstd = 1.f / sqrtf(ss / (float)nk + eps);
-  for (int c = threadIdx.x; c < nk; c += blockDim.x) stf(dst + c, k[t * ldk + c] * rstd * ldf(wk + c));
+  rms_to(q + t * ldq, nq, q_group, wq, eps, q_out + t * ldqo, red);
+  rms_to(k + t * ldk, nk, k_group, wk, eps, dst, red);
   for (int c = threadIdx.x; c < nv; c += blockDim.x) stf(dst + nk + c, v[t * ldv + c]);
 }
 
 template <typename TQ, typename TC, typename TY>
 __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(const TQ* __restrict__ q, long long ldq, int H, int G, int d,
-                                                                     int dv, const TC* __restrict__ pool,
+                                                                     int dv, int maps, const TC* __restrict__ pool,
                                                                      const int32_t* __restrict__ block_table, int max_pages,
                                                                      int page_size, const int32_t* __restrict__ pos,
-                                                                     const int32_t* __restrict__ slot, int window, float scale,
-                                                                     float softcap, const float* __restrict__ dist_bias,
+                                                                     const int32_t* __restrict__ slot, int window, int keep_first,
+                                                                     float scale, float softcap, const float* __restrict__ dist_bias,
                                                                      TY* __restrict__ out, long long ldo) {
   extern __shared__ float sm[];  // q [d] | acc [warps][dv] | m [warps] | l [warps]
-  const int t = blockIdx.x, h = blockIdx.y, kvh = h / (H / G);
+  // blockIdx.y = head * maps + map: queries and outputs are laid out [head][map][.], keys [key/value head][map][d]
+  const int t = blockIdx.x, hm = blockIdx.y, h = hm / maps, mp = hm - h * maps, kvh = h / (H / G);
   float* sq = sm;
   float* sacc = sm + d;
   float* s_m = sacc + kWinWarps * dv;
   float* s_l = s_m + kWinWarps;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) sq[c] = ldf(q + (long long)t * ldq + h * d + c);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) sq[c] = ldf(q + (long long)t * ldq + hm * d + c);
   __syncthreads();
   const int p = pos[t];
   const int first = max(0, p - window + 1);
+  const int kept = min(keep_first, first);   // keys 0 .. kept - 1 lie before the window and are seen all the same
   const int32_t* bt = block_table + (long long)slot[t] * max_pages;
-  const int W = G * (d + dv);
+  const int W = G * (maps * d + dv);
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   float m = -INFINITY, l = 0.f;
   float acc[kWinMaxPerLane];
 #pragma unroll
   for (int i = 0; i < kWinMaxPerLane; ++i) acc[i] = 0.f;
-  for (int j = first + warp; j <= p; j += kWinWarps) {
+  // the visible keys in one sequence of indices: 0 .. kept - 1, then first .. p
+  const int n_keys = kept + (p - first + 1);
+  for (int i = warp; i < n_keys; i += kWinWarps) {
+    const int j = i < kept ? i : first + (i - kept);
     const TC* row = pool + ((long long)bt[j / page_size] * page_size + j % page_size) * W;
-    const TC* kr = row + kvh * d;
-    const TC* vr = row + G * d + kvh * dv;
+    const TC* kr = row + (kvh * maps + mp) * d;
+    const TC* vr = row + G * maps * d + kvh * dv;
     float s = 0.f;
     for (int c = lane; c < d; c += 32) s = fmaf(sq[c], ldf(kr + c), s);
     s = seq_warp_sum(s) * scale;
     if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
-    if (dist_bias != nullptr) s += dist_bias[(long long)(p - j) * H + h];
+    if (dist_bias != nullptr && p - j < window) s += dist_bias[(long long)(p - j) * H + h];
     const float mn = fmaxf(m, s);
     const float corr = expf(m - mn), pj = expf(s - mn);  // m = -inf on the first key: corr = 0
     l = l * corr + pj;
 #pragma unroll
-    for (int i = 0; i < kWinMaxPerLane; ++i) {
-      const int c = lane + 32 * i;
-      if (c < dv) acc[i] = acc[i] * corr + pj * ldf(vr + c);
+    for (int i2 = 0; i2 < kWinMaxPerLane; ++i2) {
+      const int c = lane + 32 * i2;
+      if (c < dv) acc[i2] = acc[i2] * corr + pj * ldf(vr + c);
     }
     m = mn;
   }
@@ -120,7 +138,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(const TQ* _
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < kWinWarps; ++w) o += sacc[w * dv + c] * f[w];
-    stf(out + (long long)t * ldo + h * dv + c, o * inv);
+    stf(out + (long long)t * ldo + hm * dv + c, o * inv);
   }
 }
 
@@ -173,7 +191,7 @@ struct WinMmaArgs {
   const float* bias;      // [window][H] or NULL
   void* out;
   long long ldo;
-  int max_pages, page_size, H, G, d, dv, window;
+  int max_pages, page_size, H, G, d, dv, window, maps, keep_first;
   float scale, softcap;
   int bias_in_smem;       // the bias columns of this key/value head's query heads are staged in shared memory ([window][H / G])
 };
@@ -193,7 +211,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   } else {
     first_row = blockIdx.x, n_tok = 1, slot = a.slot[blockIdx.x], first_pos = a.pos[blockIdx.x];
   }
-  const int kvh = blockIdx.y, rep = a.H / a.G;
+  const int kvh = blockIdx.y / a.maps, mp = blockIdx.y - kvh * a.maps, rep = a.H / a.G;   // one score map of one key/value head
   const int n_rows = n_tok * rep;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -201,7 +219,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   for (int i = tid; i < kWmRows * qchunks; i += blockDim.x) {
     const int row = i / qchunks, c = i - row * qchunks;
     bf16_t* dst = Qs + row * pq + c * 8;
-    if (row < n_rows) w_cp_async16(wsmem_u32(dst), a.q + (long long)(first_row + row / rep) * a.ldq + (kvh * rep + row % rep) * d + c * 8);
+    if (row < n_rows) w_cp_async16(wsmem_u32(dst), a.q + (long long)(first_row + row / rep) * a.ldq + ((kvh * rep + row % rep) * a.maps + mp) * d + c * 8);
     else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
   }
   if (a.bias_in_smem)   // a lookup per score from global memory would be a chain of L2 round trips
@@ -210,17 +228,24 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   const int p0 = row0 < n_rows ? first_pos + row0 / rep : -1, p1 = row1 < n_rows ? first_pos + row1 / rep : -1;   // -1: no such row
   const int h0 = kvh * rep + row0 % rep, h1 = kvh * rep + row1 % rep;
   const int32_t* bt = a.bt + (long long)slot * a.max_pages;
-  const int k_begin = max(0, first_pos - a.window + 1), k_end = first_pos + n_tok;
-  const int roww = a.G * (d + dv);
+  // key ranges: the kept first keys that lie before the window of the item's first row (none when they touch the window: then
+  // the window range simply starts at 0), then the window range up to the item's last row
+  int k_begin = max(0, first_pos - a.window + 1);
+  const int k_end = first_pos + n_tok;
+  int kept_end = min(a.keep_first, k_begin);
+  if (kept_end == k_begin) k_begin = 0, kept_end = 0;
+  const int kept_tiles = (kept_end + kWmKeys - 1) / kWmKeys, n_tiles = kept_tiles + (k_end - k_begin + kWmKeys - 1) / kWmKeys;
+  const int roww = a.G * (a.maps * d + dv);
   // two threads per key: one page lookup per thread and tile, then 16-byte copies at a constant stride
-  auto stage = [&](int buf, int j0) {
+  auto stage = [&](int buf, int tile) {
+    const int j0 = tile < kept_tiles ? tile * kWmKeys : k_begin + (tile - kept_tiles) * kWmKeys, j_end = tile < kept_tiles ? kept_end : k_end;
     const int key = tid >> 1, half = tid & 1, j = j0 + key;
     bf16_t* kd = Ks + (buf * kWmKeys + key) * pq;
     bf16_t* vd = Vs + (buf * kWmKeys + key) * pv;
-    if (j < k_end) {
+    if (j < j_end) {
       const bf16_t* row = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * roww;
-      const bf16_t* ks = row + kvh * d;
-      const bf16_t* vs = row + a.G * d + kvh * dv;
+      const bf16_t* ks = row + (kvh * a.maps + mp) * d;
+      const bf16_t* vs = row + a.G * a.maps * d + kvh * dv;
       for (int c = half; c < qchunks; c += 2) w_cp_async16(wsmem_u32(kd + c * 8), ks + c * 8);
       for (int c = half; c < vchunks; c += 2) w_cp_async16(wsmem_u32(vd + c * 8), vs + c * 8);
     } else {
@@ -236,12 +261,12 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   const int nv = dv >> 3;
   constexpr float kLog2e = 1.4426950408889634f;
   const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
-  stage(0, k_begin);
-  int kt = 0;
-  for (int j0 = k_begin; j0 < k_end; j0 += kWmKeys, ++kt) {
+  stage(0, 0);
+  for (int kt = 0; kt < n_tiles; ++kt) {
     const int buf = kt & 1;
-    if (j0 + kWmKeys < k_end) {
-      stage(buf ^ 1, j0 + kWmKeys);   // released by the barrier that ended the previous tile
+    const int j0 = kt < kept_tiles ? kt * kWmKeys : k_begin + (kt - kept_tiles) * kWmKeys, j_end = kt < kept_tiles ? kept_end : k_end;
+    if (kt + 1 < n_tiles) {
+      stage(buf ^ 1, kt + 1);   // released by the barrier that ended the previous tile
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -276,11 +301,13 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
           const int p = e < 2 ? p0 : p1, hh = e < 2 ? h0 : h1;
           const int dist = p - key;
           float v = -INFINITY;
-          if (dist >= 0 && dist < a.window) {
+          if (key < j_end && dist >= 0 && (dist < a.window || key < a.keep_first)) {
             v = s[n][e] * a.scale;
             if (a.softcap > 0.f) v = a.softcap * tanh_approx(v * inv_cap);
-            if (a.bias_in_smem) v += sbias[dist * rep + (hh - kvh * rep)];
-            else if (a.bias != nullptr) v += __ldg(a.bias + (long long)dist * a.H + hh);
+            if (dist < a.window) {   // the table has one row per distance inside the window
+              if (a.bias_in_smem) v += sbias[dist * rep + (hh - kvh * rep)];
+              else if (a.bias != nullptr) v += __ldg(a.bias + (long long)dist * a.H + hh);
+            }
             v *= kLog2e;
           }
           s[n][e] = v;
@@ -340,8 +367,8 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   const float i0 = 1.f / l0, i1 = 1.f / l1;
-  TO* out0 = static_cast<TO*>(a.out) + (long long)(first_row + row0 / rep) * a.ldo + h0 * dv;
-  TO* out1 = static_cast<TO*>(a.out) + (long long)(first_row + row1 / rep) * a.ldo + h1 * dv;
+  TO* out0 = static_cast<TO*>(a.out) + (long long)(first_row + row0 / rep) * a.ldo + (h0 * a.maps + mp) * dv;
+  TO* out1 = static_cast<TO*>(a.out) + (long long)(first_row + row1 / rep) * a.ldo + (h1 * a.maps + mp) * dv;
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     if (j < nv) {
@@ -352,45 +379,87 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   }
 }
 
+// Two score maps of a head -> one output: o = a1 - lambda a2, o / sqrt(mean(o^2) + eps) over the head's dv values, times a constant,
+// times an elementwise gate. One CTA per row, a warp per head.
+template <typename TY>
+__global__ void __launch_bounds__(256) diff_heads_gate_kernel(const float* __restrict__ a, long long lda, int H, int dv, float lambda,
+                                                              float mult, float eps, const float* __restrict__ gate, long long ldg,
+                                                              int gate_act, TY* __restrict__ y, long long ldy) {
+  const long long t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int h = warp; h < H; h += nw) {
+    const float* a1 = a + t * lda + (long long)2 * h * dv;
+    const float* a2 = a1 + dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) {
+      const float o = a1[c] - lambda * a2[c];
+      ss = fmaf(o, o, ss);
+    }
+    ss = seq_warp_sum(ss);
+    const float f = mult / sqrtf(ss / (float)dv + eps);
+    for (int c = lane; c < dv; c += 32) {
+      float o = (a1[c] - lambda * a2[c]) * f;
+      if (gate != nullptr) {
+        const float z = gate[t * ldg + h * dv + c];
+        o *= gate_act == 2 ? 1.f / (1.f + expf(-z)) : (gate_act == 1 ? z / (1.f + expf(-z)) : z);
+      }
+      stf(y + t * ldy + h * dv + c, o);
+    }
+  }
+}
+
 }  // namespace omc
 
 using namespace omc;
 
-extern "C" int omc_qk_norm_kv_store(const float* q, long long ldq, int nq, const void* wq, const float* k, long long ldk, int nk,
-                                    const void* wk, int w_dt, const float* v, long long ldv, int nv, float eps, int T,
+extern "C" int omc_diff_heads_gate(const float* a, long long lda, int T, int H, int dv, float lambda, float mult, float eps,
+                                   const float* gate, long long ldg, int gate_act, void* y, int y_dt, long long ldy, void* stream) {
+  if (a == nullptr || y == nullptr || T < 0 || H <= 0 || dv <= 0 || gate_act < 0 || gate_act > 2)
+    return set_error(OMC_ERR_ARG, "omc_diff_heads_gate: bad argument");
+  if (T == 0) return OMC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OMC_DT_SWITCH(y_dt, TY, {
+    diff_heads_gate_kernel<TY><<<T, 256, 0, st>>>(a, lda, H, dv, lambda, mult, eps, gate, ldg, gate_act, static_cast<TY*>(y), ldy);
+  })
+  return check_launch("omc_diff_heads_gate");
+}
+
+extern "C" int omc_qk_norm_kv_store(const float* q, long long ldq, int nq, int q_group, const void* wq, const float* k, long long ldk, int nk,
+                                    int k_group, const void* wk, int w_dt, const float* v, long long ldv, int nv, float eps, int T,
                                     const int32_t* pos, const int32_t* slot, const int32_t* block_table, int max_pages, int page_size,
                                     void* pool, void* q_out, long long ldqo, int dt, void* stream) {
   if (q == nullptr || wq == nullptr || k == nullptr || wk == nullptr || v == nullptr || pos == nullptr || slot == nullptr ||
-      block_table == nullptr || pool == nullptr || q_out == nullptr || T < 0 || nq <= 0 || nk <= 0 || nv <= 0 || page_size <= 0 || max_pages <= 0)
+      block_table == nullptr || pool == nullptr || q_out == nullptr || T < 0 || nq <= 0 || nk <= 0 || nv <= 0 || page_size <= 0 || max_pages <= 0 ||
+      q_group < 0 || k_group < 0 || (q_group > 0 && nq % q_group) || (k_group > 0 && nk % k_group))
     return set_error(OMC_ERR_ARG, "omc_qk_norm_kv_store: bad argument");
   if (T == 0) return OMC_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   OMC_DT_SWITCH(w_dt, TW, OMC_DT_SWITCH(dt, TC, {
-    qk_norm_kv_store_kernel<TW, TC><<<T, 256, 0, st>>>(q, ldq, nq, static_cast<const TW*>(wq), k, ldk, nk, static_cast<const TW*>(wk), v,
+    qk_norm_kv_store_kernel<TW, TC><<<T, 256, 0, st>>>(q, ldq, nq, q_group, static_cast<const TW*>(wq), k, ldk, nk, k_group, static_cast<const TW*>(wk), v,
                                                        ldv, nv, eps, pos, slot, block_table, max_pages, page_size,
                                                        static_cast<TC*>(pool), static_cast<TC*>(q_out), ldqo);
   }))
   return check_launch("omc_qk_norm_kv_store");
 }
 
-extern "C" int omc_window_attn(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool, int dt,
+extern "C" int omc_window_attn(const void* q, long long ldq, int T, int H, int G, int d, int dv, int maps, const void* pool, int dt,
                                const int32_t* block_table, int max_pages, int page_size, const int32_t* pos, const int32_t* slot,
-                               int window, float scale, float softcap, const float* dist_bias, void* out, int out_dt, long long ldo,
-                               void* stream) {
+                               int window, int keep_first, float scale, float softcap, const float* dist_bias, void* out, int out_dt,
+                               long long ldo, void* stream) {
   if (q == nullptr || pool == nullptr || block_table == nullptr || pos == nullptr || slot == nullptr || out == nullptr || T < 0 ||
-      H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || window < 1 || page_size <= 0 || max_pages <= 0)
+      H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || maps < 1 || window < 1 || keep_first < 0 || page_size <= 0 || max_pages <= 0)
     return set_error(OMC_ERR_ARG, "omc_window_attn: bad argument");
   if (T == 0) return OMC_OK;
   if (dv > 32 * kWinMaxPerLane) return set_error(OMC_ERR_SHAPE, "omc_window_attn: value width above 256");
-  if (H > 65535) return set_error(OMC_ERR_SHAPE, "omc_window_attn: more than 65535 heads");
+  if ((long long)H * maps > 65535) return set_error(OMC_ERR_SHAPE, "omc_window_attn: more than 65535 heads");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t smem = sizeof(float) * ((size_t)d + (size_t)kWinWarps * dv + 2 * kWinWarps);
   if (smem > 48 * 1024) return set_error(OMC_ERR_SHAPE, "omc_window_attn: head width too large");
   OMC_DT_SWITCH(dt, TC, OMC_DT_SWITCH(out_dt, TY, {
-    window_attn_kernel<TC, TC, TY><<<dim3(T, H), kWinWarps * 32, smem, st>>>(static_cast<const TC*>(q), ldq, H, G, d, dv,
-                                                                            static_cast<const TC*>(pool), block_table, max_pages,
-                                                                            page_size, pos, slot, window, scale, softcap, dist_bias,
-                                                                            static_cast<TY*>(out), ldo);
+    window_attn_kernel<TC, TC, TY><<<dim3(T, H * maps), kWinWarps * 32, smem, st>>>(static_cast<const TC*>(q), ldq, H, G, d, dv, maps,
+                                                                                   static_cast<const TC*>(pool), block_table, max_pages,
+                                                                                   page_size, pos, slot, window, keep_first, scale, softcap,
+                                                                                   dist_bias, static_cast<TY*>(out), ldo);
   }))
   return check_launch("omc_window_attn");
 }
@@ -401,20 +470,20 @@ extern "C" int omc_window_attn_mma_ok(int H, int G, int d, int dv) {
   return (d % 16 == 0 && dv % 16 == 0 && d >= 16 && d <= 256 && dv >= 16 && dv <= 128 && rep <= 64 && 64 % rep == 0) ? 1 : 0;
 }
 
-extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool,
+extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d, int dv, int maps, const void* pool,
                                    const int32_t* block_table, int max_pages, int page_size, const int32_t* items, int n_items,
-                                   const int32_t* pos, const int32_t* slot, int window, float scale, float softcap,
+                                   const int32_t* pos, const int32_t* slot, int window, int keep_first, float scale, float softcap,
                                    const float* dist_bias, void* out, int out_dt, long long ldo, void* stream) {
-  if (q == nullptr || pool == nullptr || block_table == nullptr || out == nullptr || T < 0 || window < 1 || page_size <= 0 ||
+  if (q == nullptr || pool == nullptr || block_table == nullptr || out == nullptr || T < 0 || window < 1 || maps < 1 || keep_first < 0 || page_size <= 0 ||
       max_pages <= 0 || (items == nullptr && (pos == nullptr || slot == nullptr)) || n_items < 0)
     return set_error(OMC_ERR_ARG, "omc_window_attn_mma: bad argument");
   if (!omc_window_attn_mma_ok(H, G, d, dv) || ldq % 8 || ldo % 2 || reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(pool) % 16)
     return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: shape or alignment not supported (see omc_window_attn_mma_ok)");
   const int n = items != nullptr ? n_items : T;
   if (n == 0) return OMC_OK;
-  if (G > 65535) return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: more than 65535 key/value heads");
+  if ((long long)G * maps > 65535) return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: more than 65535 key/value heads");
   WinMmaArgs a{static_cast<const bf16_t*>(q), ldq, static_cast<const bf16_t*>(pool), block_table, items, pos, slot, dist_bias, out, ldo,
-               max_pages, page_size, H, G, d, dv, window, scale, softcap, 0};
+               max_pages, page_size, H, G, d, dv, window, maps, keep_first, scale, softcap, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   size_t smem = sizeof(bf16_t) * ((size_t)kWmRows * (d + 8) + 2 * (size_t)kWmKeys * (d + 8) + 2 * (size_t)kWmKeys * (dv + 8));
   const size_t bias_bytes = sizeof(float) * (size_t)window * (H / G);
@@ -422,7 +491,7 @@ extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, i
     a.bias_in_smem = 1;
     smem += bias_bytes;
   }
-  dim3 grid(n, G);
+  dim3 grid(n, G * maps);
 #define OMC_WIN_LAUNCH(NV, TO)                                                                                      \
   do {                                                                                                              \
     static bool attr_done[kMaxDevices] = {};                                                                        \

@@ -17,7 +17,8 @@ from .lib import OmcError, _need_cuda, _ptr, _stream
 
 _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
 DT_F32, DT_BF16 = 0, 1
-ACT_NONE, ACT_RELU2, ACT_GELU_TANH = 0, 1, 2
+ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_GELU_ERF, ACT_CLAMP_SWISH = 0, 1, 2, 3, 4
+CONV_LINEAR, CONV_SILU = 0, 1
 LINEAR_TILE = 64  # rows per tile of omc_linear's tile -> group table
 
 SIGNATURES = {
@@ -25,15 +26,17 @@ SIGNATURES = {
     "omc_linear": (_I, [_P, _I, _L, _L, _P, _I, _L, _L, _P, _I, _L, _L, _I, _I, _I, _I, _F, _I, _P, _L, _P]),
     "omc_linear_bias": (_I, [_P, _I, _L, _L, _P, _I, _L, _L, _P, _I, _L, _L, _I, _I, _I, _I, _F, _I, _P, _L, _P, _L, _P]),
     "omc_post_norm_residual": (_I, [_P, _L, _P, _P, _L, _P, _P, _I, _F, _F, _P, _L, _P, _P, _I, _L, _I, _I, _P]),
-    "omc_glu_mul": (_I, [_P, _I, _L, _I, _I, _I, _P, _I, _L, _P]),
-    "omc_causal_conv_silu": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _F, _I, _F, _I, _P]),
+    "omc_glu_mul": (_I, [_P, _I, _L, _I, _I, _I, _F, _F, _F, _P, _I, _L, _P]),
+    "omc_embed_sinusoid": (_I, [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P, _L, _P]),
+    "omc_diff_heads_gate": (_I, [_P, _L, _I, _I, _I, _F, _F, _F, _P, _L, _I, _P, _I, _L, _P]),
+    "omc_causal_conv": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _F, _I, _P]),
     "omc_linear_state_scan": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _P]),
     "omc_map_rows": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _P]),
     "omc_gated_rms_rows": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _L, _I, _P, _I, _L, _P]),
-    "omc_qk_norm_kv_store": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _I, _P, _L, _I, _F, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _P]),
-    "omc_window_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _F, _F, _P, _P, _I, _L, _P]),
+    "omc_qk_norm_kv_store": (_I, [_P, _L, _I, _I, _P, _P, _L, _I, _I, _P, _I, _P, _L, _I, _F, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _P]),
+    "omc_window_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _F, _F, _P, _P, _I, _L, _P]),
     "omc_window_attn_mma_ok": (_I, [_I, _I, _I, _I]),
-    "omc_window_attn_mma": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _F, _F, _P, _P, _I, _L, _P]),
+    "omc_window_attn_mma": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _I, _F, _F, _P, _P, _I, _L, _P]),
     "omc_embed_scale": (_I, [_P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _I, _L, _P]),
     "omc_rms_rows": (_I, [_P, _L, _P, _I, _I, _F, _P, _I, _L, _I, _I, _P]),
     "omc_norm_residual": (_I, [_P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
@@ -44,10 +47,10 @@ SIGNATURES = {
     "omc_latent_attn": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _P]),
     "omc_latent_attn_mma": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _I, _P, _P, _P]),
     "omc_latent_decode_items": (_I, [_P, _P, _I, _I, _I, _P, _P, _P]),
-    "omc_router_topk": (_I, [_P, _L, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P]),
+    "omc_router_topk": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P]),
     "omc_moe_plan_tiles": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "omc_moe_scatter_rows": (_I, [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P]),
-    "omc_moe_combine_norm": (_I, [_P, _L, _P, _P, _I, _P, _P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
+    "omc_moe_combine_norm": (_I, [_P, _L, _P, _P, _I, _P, _P, _L, _P, _I, _F, _P, _L, _P, _P, _I, _L, _I, _I, _P]),
 }
 
 _lib = None
@@ -122,6 +125,23 @@ def embed_scale(ids: torch.Tensor, table: torch.Tensor, scale: float, h32: torch
     rc = load().omc_embed_scale(_ptr(ids), T, _ptr(table), _dt(table), C, table.shape[0], scale, _ptr(h32), h32.stride(0),
                                 _ptr(xb), _dt(xb), xb.stride(0) if xb is not None else 0, _stream())
     _check(rc, "omc_embed_scale")
+
+
+def sinusoid_frequencies(C: int, base: float, device) -> torch.Tensor:
+    """float64 [ceil(C / 2)] on the device: f_i = base^(-2i / C), the table omc_embed_sinusoid reads."""
+    n = (C + 1) // 2
+    return torch.tensor([base ** (-2.0 * i / C) for i in range(n)], dtype=torch.float64).to(device)
+
+
+def embed_sinusoid(ids: torch.Tensor, pos: torch.Tensor, table: torch.Tensor, scale: float, freq: torch.Tensor, h32: torch.Tensor):
+    """h32[t] = table[ids[t]] * scale + (sin, cos)(pos[t] * freq) interleaved (entry 2i: sin, 2i + 1: cos)."""
+    _need_cuda(ids, pos, table, freq, h32)
+    T, C = ids.numel(), table.shape[1]
+    assert ids.dtype == torch.int32 and pos.dtype == torch.int32 and h32.dtype == torch.float32 and table.is_contiguous()
+    assert freq.dtype == torch.float64 and freq.is_contiguous() and freq.numel() >= (C + 1) // 2
+    rc = load().omc_embed_sinusoid(_ptr(ids), _ptr(pos), T, _ptr(table), _dt(table), C, table.shape[0], scale, _ptr(freq), _ptr(h32),
+                                   h32.stride(0), _stream())
+    _check(rc, "omc_embed_sinusoid")
 
 
 def rms_rows(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, out: torch.Tensor, one_plus: bool = False, n: Optional[int] = None):
@@ -302,12 +322,15 @@ def latent_attn_mma(qcat: torch.Tensor, r: int, dr: int, pool: torch.Tensor, blo
 
 
 def router_topk(z: torch.Tensor, e_tot: int, experts: int, top: int, correction: Optional[torch.Tensor], has_gate: bool,
-                ids: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], counts: torch.Tensor):
-    _need_cuda(z, correction, ids, w, gate, counts)
+                ids: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], counts: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, renorm: bool = False):
+    """bias: fp32 [e_tot] added to the logits; renorm: the weights of the chosen are divided by their sum (softmax over the chosen)."""
+    _need_cuda(z, correction, bias, ids, w, gate, counts)
     assert z.dtype == torch.float32 and ids.dtype == torch.int32 and w.dtype == torch.float32 and counts.dtype == torch.int32
     assert correction is None or correction.dtype == torch.float32
-    rc = load().omc_router_topk(_ptr(z), z.stride(0), z.shape[0], e_tot, experts, top, _ptr(correction), 1 if has_gate else 0,
-                                _ptr(ids), _ptr(w), _ptr(gate), _ptr(counts), _stream())
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == e_tot)
+    rc = load().omc_router_topk(_ptr(z), z.stride(0), z.shape[0], e_tot, experts, top, _ptr(correction), _ptr(bias), 1 if renorm else 0,
+                                1 if has_gate else 0, _ptr(ids), _ptr(w), _ptr(gate), _ptr(counts), _stream())
     _check(rc, "omc_router_topk")
 
 
@@ -330,11 +353,14 @@ def moe_scatter_rows(x, ids, top: int, experts: int, seg_start, cursor, slot_of,
     _check(rc, "omc_moe_scatter_rows")
 
 
-def moe_combine_norm(ys: Optional[torch.Tensor], slot_of, w, top: int, gate, ysh: Optional[torch.Tensor], nw, eps: float, h32, xb):
-    _need_cuda(ys, slot_of, w, gate, ysh, nw, h32, xb)
+def moe_combine_norm(ys: Optional[torch.Tensor], slot_of, w, top: int, gate, ysh: Optional[torch.Tensor], nw, eps: float, h32, xb,
+                     w_next: Optional[torch.Tensor] = None):
+    """w_next: xb receives h32 / rms(h32) * (1 + w_next), the next sublayer's normed input, instead of the rounded h32."""
+    _need_cuda(ys, slot_of, w, gate, ysh, nw, h32, xb, w_next)
+    assert w_next is None or w_next.dtype == nw.dtype
     rc = load().omc_moe_combine_norm(_ptr(ys), ys.stride(0) if ys is not None else 0, _ptr(slot_of), _ptr(w), top, _ptr(gate),
                                      _ptr(ysh), ysh.stride(0) if ysh is not None else 0, _ptr(nw), _dt(nw), eps, _ptr(h32),
-                                     h32.stride(0), _ptr(xb), _dt(xb), xb.stride(0) if xb is not None else 0, h32.shape[0],
+                                     h32.stride(0), _ptr(w_next), _ptr(xb), _dt(xb), xb.stride(0) if xb is not None else 0, h32.shape[0],
                                      h32.shape[1], _stream())
     _check(rc, "omc_moe_combine_norm")
 
@@ -353,11 +379,13 @@ def post_norm_residual(y1: torch.Tensor, w_post: torch.Tensor, eps: float, mult:
     _check(rc, "omc_post_norm_residual")
 
 
-def glu_mul(z: torch.Tensor, n: int, act: int, out: torch.Tensor):
-    """out[:, c] = act(z[:, c]) * z[:, n + c]."""
+def glu_mul(z: torch.Tensor, n: int, act: int, out: torch.Tensor, limit: float = 0.0, slope: float = 1.0, shift: float = 0.0):
+    """out[:, c] = act(z[:, c]) * z[:, n + c]. ACT_CLAMP_SWISH: g = min(z[:, c], limit), u = clamp(z[:, n + c], -limit, limit),
+    out = g * sigmoid(slope * g) * (u + shift)."""
     _need_cuda(z, out)
     assert z.stride(1) == 1 and out.stride(1) == 1 and z.shape[1] >= 2 * n
-    rc = load().omc_glu_mul(_ptr(z), _dt(z), z.stride(0), z.shape[0], n, act, _ptr(out), _dt(out), out.stride(0), _stream())
+    rc = load().omc_glu_mul(_ptr(z), _dt(z), z.stride(0), z.shape[0], n, act, limit, slope, shift, _ptr(out), _dt(out), out.stride(0),
+                            _stream())
     _check(rc, "omc_glu_mul")
     return out
 
@@ -370,21 +398,27 @@ MAP_SILU, MAP_DECAY = 1, 2
 
 def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, state: Optional[torch.Tensor],
                      y: torch.Tensor, unit_channels: int = 0, unit_group: int = 0, unit_eps: float = 1e-6, scaled_channels: int = 0,
-                     unit_mult: float = 1.0, single_rows: bool = False):
+                     unit_mult: float = 1.0, single_rows: bool = False, act: int = CONV_SILU):
     """x fp32 [T, >= ch] (a column slice is fine), w [ch, taps], state fp32 [slots, taps - 1, ch] -> y fp32 [T, ch].
-    single_rows: every row is a request of its own (one launch instead of two)."""
+    single_rows: every row is a request of its own (one launch instead of two). act: CONV_SILU, or CONV_LINEAR for the weighted
+    sum itself (`causal_conv`)."""
     _need_cuda(x, w, pos, slot, state, y)
     ch, taps = w.shape
     assert x.dtype == torch.float32 and y.dtype == torch.float32 and x.stride(1) == 1 and y.stride(1) == 1 and w.is_contiguous()
     assert pos.dtype == torch.int32 and slot.dtype == torch.int32
     assert taps == 1 or (state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, ch))
-    rc = load().omc_causal_conv_silu(_ptr(x), x.stride(0), x.shape[0], ch, _ptr(w), _dt(w), taps, _ptr(pos), _ptr(slot), _ptr(state),
-                                     _ptr(y), y.stride(0), unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
-                                     1 if single_rows else 0, _stream())
-    _check(rc, "omc_causal_conv_silu")
+    rc = load().omc_causal_conv(_ptr(x), x.stride(0), x.shape[0], ch, _ptr(w), _dt(w), taps, _ptr(pos), _ptr(slot), _ptr(state),
+                                _ptr(y), y.stride(0), act, unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
+                                1 if single_rows else 0, _stream())
+    _check(rc, "omc_causal_conv")
     if taps > 1 and not single_rows:
         _core.add_launches(1)
     return y
+
+
+def causal_conv(x, w, pos, slot, state, y, single_rows: bool = False):
+    """The causal convolution alone (no activation, no unit vectors)."""
+    return causal_conv_silu(x, w, pos, slot, state, y, single_rows=single_rows, act=CONV_LINEAR)
 
 
 def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_begin: torch.Tensor,
@@ -422,27 +456,36 @@ def gated_rms_rows(x: torch.Tensor, groups: int, n: int, w: torch.Tensor, eps: f
 
 # ---- windowed attention over a paged key/value cache
 def qk_norm_kv_store(q: torch.Tensor, wq: torch.Tensor, k: torch.Tensor, wk: torch.Tensor, v: torch.Tensor, eps: float, pos, slot,
-                     block_table: torch.Tensor, page_size: int, pool: torch.Tensor, q_out: torch.Tensor):
+                     block_table: torch.Tensor, page_size: int, pool: torch.Tensor, q_out: torch.Tensor, group: int = 0):
+    """group 0: one norm over all query (key) columns, weights as wide as the projections; group > 0: one norm per `group` columns
+    with weights [group] shared by the groups (q and k are then given with their true widths)."""
     _need_cuda(q, wq, k, wk, v, pos, slot, block_table, pool, q_out)
-    nq, nk, nv = wq.numel(), wk.numel(), v.shape[1]
+    nq, nk, nv = (wq.numel(), wk.numel(), v.shape[1]) if group == 0 else (q.shape[1], k.shape[1], v.shape[1])
+    assert group == 0 or (wq.numel() == group and wk.numel() == group)
     assert q.dtype == k.dtype == v.dtype == torch.float32 and q.stride(1) == k.stride(1) == v.stride(1) == 1
     assert pool.is_contiguous() and pool.shape[-1] == nk + nv and pool.dtype == q_out.dtype and wq.dtype == wk.dtype
     assert block_table.dtype == torch.int32 and block_table.is_contiguous() and q_out.stride(1) == 1
-    rc = load().omc_qk_norm_kv_store(_ptr(q), q.stride(0), nq, _ptr(wq), _ptr(k), k.stride(0), nk, _ptr(wk), _dt(wq), _ptr(v), v.stride(0),
+    rc = load().omc_qk_norm_kv_store(_ptr(q), q.stride(0), nq, group, _ptr(wq), _ptr(k), k.stride(0), nk, group, _ptr(wk), _dt(wq), _ptr(v), v.stride(0),
                                      nv, eps, q.shape[0], _ptr(pos), _ptr(slot), _ptr(block_table), block_table.shape[1], page_size,
                                      _ptr(pool), _ptr(q_out), q_out.stride(0), _dt(pool), _stream())
     _check(rc, "omc_qk_norm_kv_store")
 
 
+WINDOW_ALL = 1 << 30   # a window that never ends: plain causal attention
+
+
 def window_attn(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int, pos, slot,
-                window: int, scale: float, softcap: float, dist_bias: Optional[torch.Tensor], out: torch.Tensor):
-    """q [T, H * d] and pool of one dtype -> out [T, H * dv]."""
+                window: int, scale: float, softcap: float, dist_bias: Optional[torch.Tensor], out: torch.Tensor, maps: int = 1,
+                keep_first: int = 0):
+    """q [T, H * maps * d] and pool of one dtype -> out [T, H * maps * dv]. maps: score maps per head (queries and keys of their
+    own, shared values); keep_first: the first keys of a sequence stay visible behind the window."""
     _need_cuda(q, pool, block_table, pos, slot, dist_bias, out)
-    assert q.dtype == pool.dtype and q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous() and pool.shape[-1] == G * (d + dv)
+    assert q.dtype == pool.dtype and q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
+    assert pool.shape[-1] == G * (maps * d + dv)
     assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape == (window, H))
-    rc = load().omc_window_attn(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, _ptr(pool), _dt(pool), _ptr(block_table),
-                                block_table.shape[1], page_size, _ptr(pos), _ptr(slot), window, scale, softcap, _ptr(dist_bias), _ptr(out),
-                                _dt(out), out.stride(0), _stream())
+    rc = load().omc_window_attn(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, maps, _ptr(pool), _dt(pool), _ptr(block_table),
+                                block_table.shape[1], page_size, _ptr(pos), _ptr(slot), window, keep_first, scale, softcap,
+                                _ptr(dist_bias), _ptr(out), _dt(out), out.stride(0), _stream())
     _check(rc, "omc_window_attn")
     return out
 
@@ -467,17 +510,30 @@ def window_attn_items(portions, rep: int, device) -> torch.Tensor:
 
 def window_attn_mma(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int,
                     items: Optional[torch.Tensor], pos, slot, window: int, scale: float, softcap: float,
-                    dist_bias: Optional[torch.Tensor], out: torch.Tensor):
-    """items None: every row of q is a request of its own at (slot[t], pos[t])."""
+                    dist_bias: Optional[torch.Tensor], out: torch.Tensor, maps: int = 1, keep_first: int = 0):
+    """items None: every row of q is a request of its own at (slot[t], pos[t]). maps / keep_first as in window_attn."""
     _need_cuda(q, pool, block_table, items, pos, slot, dist_bias, out)
     assert q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
-    assert pool.is_contiguous() and pool.shape[-1] == G * (d + dv) and block_table.is_contiguous()
+    assert pool.is_contiguous() and pool.shape[-1] == G * (maps * d + dv) and block_table.is_contiguous()
     assert items is None or (items.dtype == torch.int32 and items.is_contiguous() and items.shape[1] == 4)
     assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape == (window, H))
-    rc = load().omc_window_attn_mma(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, _ptr(pool), _ptr(block_table), block_table.shape[1],
+    rc = load().omc_window_attn_mma(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, maps, _ptr(pool), _ptr(block_table), block_table.shape[1],
                                     page_size, _ptr(items), items.shape[0] if items is not None else 0, _ptr(pos), _ptr(slot), window,
-                                    scale, softcap, _ptr(dist_bias), _ptr(out), _dt(out), out.stride(0), _stream())
+                                    keep_first, scale, softcap, _ptr(dist_bias), _ptr(out), _dt(out), out.stride(0), _stream())
     _check(rc, "omc_window_attn_mma")
+    return out
+
+
+def diff_heads_gate(a: torch.Tensor, H: int, dv: int, lam: float, mult: float, eps: float, gate: Optional[torch.Tensor], gate_act: int,
+                    out: torch.Tensor):
+    """a fp32 [T, H * 2 * dv] (two score maps per head, side by side) -> out [T, H * dv]:
+    o = a1 - lam * a2;  o / sqrt(mean(o^2) + eps) * mult * act(gate)."""
+    _need_cuda(a, gate, out)
+    assert a.dtype == torch.float32 and a.stride(1) == 1 and out.stride(1) == 1 and a.shape[1] >= 2 * H * dv
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
+    rc = load().omc_diff_heads_gate(_ptr(a), a.stride(0), a.shape[0], H, dv, lam, mult, eps, _ptr(gate),
+                                    gate.stride(0) if gate is not None else 0, gate_act, _ptr(out), _dt(out), out.stride(0), _stream())
+    _check(rc, "omc_diff_heads_gate")
     return out
 
 
