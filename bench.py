@@ -300,6 +300,10 @@ def main():
     ap.add_argument("--tifisun", action="append", choices=["s", "m"], help="instead of the default workload: the Tifisun decoder at "
                     "this size (random weights) beside the dense Qwen2 decoder at equal size - prefill and decode throughput and "
                     "the new kernels against their rooflines (tools/bench_tifisun.py); one JSON line per size")
+    ap.add_argument("--fofisun", action="append", choices=["s", "m"], help="instead of the default workload: the Fofisun decoder at "
+                    "this size (random weights; dense and mixture-of-experts feed-forwards) beside the Tifisun decoder at equal size - "
+                    "prefill and decode throughput and the new kernels against their rooflines (tools/bench_fofisun.py); one JSON "
+                    "line per size")
     ap.add_argument("--pixel-shuffle", type=float, default=1.0, help="mm_pixel_shuffle_ratio (1.0 = reference behaviour)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -319,6 +323,14 @@ def main():
         torch.cuda.set_device(0)
         for size in args.tifisun:
             print(json.dumps(measure_tifisun(size, steps=max(args.steps, 8))), flush=True)
+        return
+
+    if args.fofisun:
+        import torch
+        from tools.bench_fofisun import measure as measure_fofisun
+        torch.cuda.set_device(0)
+        for size in args.fofisun:
+            print(json.dumps(measure_fofisun(size, steps=max(args.steps, 8))), flush=True)
         return
 
     import torch

@@ -1,4 +1,4 @@
-"""The linear layer of the sequence-step decoders (Voduzen, Tifisun): which kernel multiplies which matrix.
+"""The linear layer of the sequence-step decoders (Voduzen, Tifisun, Fofisun): which kernel multiplies which matrix.
 
 Matrices with at least TENSOR_GEMM_MIN_WEIGHT elements go through the tcgen05 GEMM of the core library when the operands are bf16
 and the dimensions are multiples of 8; below it a launch is latency-bound either way and the kernel of the sequence-step library
@@ -18,6 +18,7 @@ from .. import lib, seqlib
 
 TENSOR_GEMM_MIN_WEIGHT = 1 << 20
 SKINNY_GEMM_MIN_WEIGHT = 1 << 17
+_TENSOR_EPILOGUES = {seqlib.ACT_RELU2: lib.EPI_RELU2, seqlib.ACT_GELU_ERF: lib.EPI_GELU}   # activations the tensor-core GEMMs apply themselves
 
 
 def dense_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *, tensor_gemm: bool, act: int = seqlib.ACT_NONE,
@@ -27,9 +28,8 @@ def dense_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *, te
     N = w.shape[0]
     big = N * K >= (SKINNY_GEMM_MIN_WEIGHT if M <= lib.SKINNY_MAX_M else TENSOR_GEMM_MIN_WEIGHT)
     if (tensor_gemm and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and big and N % 8 == 0 and K % 8 == 0
-            and x.stride(0) % 8 == 0 and (act == seqlib.ACT_NONE or (act == seqlib.ACT_RELU2 and out_dtype == torch.bfloat16))):
-        y = lib.gemm(x, w, bias=bias, out_f32=out_dtype == torch.float32,
-                     epi=lib.EPI_RELU2 if act == seqlib.ACT_RELU2 else lib.EPI_NONE)
+            and x.stride(0) % 8 == 0 and (act == seqlib.ACT_NONE or (act in _TENSOR_EPILOGUES and out_dtype == torch.bfloat16))):
+        y = lib.gemm(x, w, bias=bias, out_f32=out_dtype == torch.float32, epi=_TENSOR_EPILOGUES.get(act, lib.EPI_NONE))
         return y if alpha == 1.0 else y.mul_(alpha)
     out = torch.empty(M, N, device=x.device, dtype=out_dtype)
     return seqlib.linear(x, w, out, alpha=alpha, act=act, bias=bias)
