@@ -175,6 +175,15 @@ int omc_causal_conv(const float* x, long long ldx, int T, int ch, const void* w,
                     const int32_t* slot, float* state, float* y, long long ldy, int act, int unit_channels, int unit_group,
                     float unit_eps, int scaled_channels, float unit_mult, int single_rows, void* stream);
 
+/* omc_causal_conv (linear) + omc_qk_norm_kv_store (per group) in one launch: x fp32 [T, ch] holds the projected q | k | v rows
+ * (nq + nk + the rest), w [ch, taps] the three convolutions stacked, state the ring [slots][taps - 1][ch]. The convolved queries
+ * and keys get an RMS norm per `group` channels with the weights wq / wk [group] (of w_dt); q_out [T, nq] and the cache row
+ * [k | v] of (slot[t], pos[t]) in pool [pages][page_size][ch - nq] are of dtype dt. single_rows as in omc_causal_conv_silu. */
+int omc_conv_qk_norm_kv_store(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps, const int32_t* pos,
+                              const int32_t* slot, float* state, int nq, int nk, int group, const void* wq, const void* wk, float eps,
+                              const int32_t* block_table, int max_pages, int page_size, void* pool, void* q_out, long long ldqo, int dt,
+                              int single_rows, void* stream);
+
 /* Linear-state recurrence per head with an fp32 state S [dim, vdim] in state[slot][head]:
  *   S <- diag(g_t) S;  u_t = beta_t (v_t - S^T k_t) (beta != NULL) or v_t;  S <- S + k_t u_t^T;  o_t = S^T q_t.
  * decay_mode 0: g = decay_const[head]; 1: g = exp(-exp(A_log[head]) softplus(a[t, head] + dt_bias[head])); 2: one decay per key

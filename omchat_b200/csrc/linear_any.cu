@@ -85,6 +85,49 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
   }
 }
 
+// ---- a few outputs per row (routers, gates, low-rank factors): the tile kernels would leave such a product to a handful of CTAs
+// that each walk all of K. Here a CTA takes 8 rows, holds them in shared memory as fp32, and every warp owns one output column at a
+// time: it reads that row of W once and feeds 8 accumulators, the lanes striding K; a shuffle tree finishes the sums. The order of
+// a sum depends on K alone.
+constexpr int kNarrowRows = 8, kNarrowMaxN = 64, kNarrowMaxK = 6144;
+
+template <typename TX, typename TW, typename TY>
+__global__ void __launch_bounds__(256) linear_narrow_kernel(LinearArgs a) {
+  extern __shared__ float nxs[];   // [kNarrowRows][K]
+  const int m0 = blockIdx.x * kNarrowRows, nr = min(kNarrowRows, a.M - m0);
+  const TX* X = static_cast<const TX*>(a.X) + (long long)blockIdx.z * a.sx;
+  const TW* W = static_cast<const TW*>(a.W) + (long long)blockIdx.z * a.sw;
+  TY* Y = static_cast<TY*>(a.Y) + (long long)blockIdx.z * a.sy;
+  const int K = a.K;
+  for (int e = threadIdx.x; e < kNarrowRows * K; e += blockDim.x) {
+    const int r = e / K, k = e - r * K;
+    nxs[e] = r < nr ? ldf(X + (long long)(m0 + r) * a.ldx + k) : 0.f;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int n = warp; n < a.N; n += 8) {
+    const TW* wr = W + (long long)n * a.ldw;
+    float acc[kNarrowRows];
+#pragma unroll
+    for (int r = 0; r < kNarrowRows; ++r) acc[r] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float wv = ldf(wr + k);
+#pragma unroll
+      for (int r = 0; r < kNarrowRows; ++r) acc[r] = fmaf(nxs[r * K + k], wv, acc[r]);
+    }
+    float mine = 0.f;
+#pragma unroll
+    for (int r = 0; r < kNarrowRows; ++r) {
+      const float v = seq_warp_sum(acc[r]);
+      if (lane == r) mine = v;
+    }
+    if (lane < nr) {
+      const float b = a.bias != nullptr ? ldf(static_cast<const TW*>(a.bias) + blockIdx.z * a.sbias + n) : 0.f;
+      stf(Y + (long long)(m0 + lane) * a.ldy + n, apply_act(mine * a.alpha + b, a.act));
+    }
+  }
+}
+
 // ---- bf16 x bf16 on the tensor pipe (mma.sync.m16n8k16): the same interface for operands whose rows start on 16-byte boundaries.
 // 128 x 128 output tile, K slices of 32 double-buffered with cp.async, 8 warps of 64 x 32. It serves the batched per-head products
 // of latent attention (absorbing W_uk into the query, W_uv after the attention), whose heads are column slices of one buffer.
@@ -196,8 +239,31 @@ static int launch_linear_mma(const LinearArgs& a, int y_dt, int batch, cudaStrea
   return check_launch("omc_linear");
 }
 
+template <typename TX, typename TW, typename TY>
+static int launch_narrow_typed(const LinearArgs& a, int batch, cudaStream_t st) {
+  const size_t smem = sizeof(float) * kNarrowRows * (size_t)a.K;
+  if (smem > 48 * 1024) {
+    static bool attr_done[kMaxDevices] = {};
+    if (!attr_done[cur_device()]) {
+      cudaFuncSetAttribute(linear_narrow_kernel<TX, TW, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * kNarrowRows * kNarrowMaxK));
+      attr_done[cur_device()] = true;
+    }
+  }
+  linear_narrow_kernel<TX, TW, TY><<<dim3((a.M + kNarrowRows - 1) / kNarrowRows, 1, batch), 256, smem, st>>>(a);
+  return check_launch("omc_linear");
+}
+
+template <typename TX, typename TW>
+static int launch_narrow(const LinearArgs& a, int y_dt, int batch, cudaStream_t st) {
+  if (y_dt == OMC_DT_F32) return launch_narrow_typed<TX, TW, float>(a, batch, st);
+  if (y_dt == OMC_DT_BF16) return launch_narrow_typed<TX, TW, bf16_t>(a, batch, st);
+  return set_error(OMC_ERR_ARG, "omc_linear: unknown output dtype");
+}
+
 template <typename TX, typename TW>
 static int launch_linear(const LinearArgs& a, int y_dt, int batch, cudaStream_t st) {
+  // few outputs over a long K: the choice depends on widths only, never on M
+  if (a.tile_group == nullptr && a.N <= kNarrowMaxN && a.K <= kNarrowMaxK && a.K >= 4 * a.N) return launch_narrow<TX, TW>(a, y_dt, batch, st);
   dim3 grid((a.N + kLinBN - 1) / kLinBN, (a.M + kLinBM - 1) / kLinBM, batch);
   if (y_dt == OMC_DT_F32) linear_tile_kernel<TX, TW, float><<<grid, 256, 0, st>>>(a);
   else if (y_dt == OMC_DT_BF16) linear_tile_kernel<TX, TW, bf16_t><<<grid, 256, 0, st>>>(a);
@@ -225,7 +291,8 @@ extern "C" int omc_linear_bias(const void* X, int x_dt, long long ldx, long long
   if (x_dt == OMC_DT_F32 && w_dt == OMC_DT_BF16) return launch_linear<float, bf16_t>(a, y_dt, batch, st);
   if (x_dt == OMC_DT_BF16 && w_dt == OMC_DT_BF16) {
     // the choice depends on layout and widths only, never on M: a row is computed by the same kernel in every batch
-    if (mma_operands_ok(a) && (long long)N * K >= 4096) return launch_linear_mma(a, y_dt, batch, st);
+    const bool narrow = tile_group == nullptr && N <= kNarrowMaxN && K <= kNarrowMaxK && K >= 4 * N;
+    if (!narrow && mma_operands_ok(a) && (long long)N * K >= 4096) return launch_linear_mma(a, y_dt, batch, st);
     return launch_linear<bf16_t, bf16_t>(a, y_dt, batch, st);
   }
   return set_error(OMC_ERR_ARG, "omc_linear: operand dtypes must be (f32, f32), (f32, bf16) or (bf16, bf16)");

@@ -85,6 +85,74 @@ __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __re
   }
 }
 
+// The same convolution (no activation) in front of an attention: the first nq + nk channels are queries and keys that get an RMS norm
+// per `group` channels (a head, or one score map of a head) with the weights wq / wk [group]; queries go to q_out, normed keys and the
+// remaining channels (values) to the row of (slot, position) in the paged cache [pages][page_size][ch - nq]. One launch instead of
+// convolution, norm and append, and the convolved rows never travel through memory.
+template <typename TW, typename TC>
+__global__ void __launch_bounds__(256) conv_qk_norm_store_kernel(const float* __restrict__ x, long long ldx, int T, int ch, int ch_block,
+                                                                 int rows_per_cta, const TW* __restrict__ w, int taps,
+                                                                 const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
+                                                                 float* __restrict__ state, int nq, int nk, int group,
+                                                                 const TW* __restrict__ wq, const TW* __restrict__ wk, float eps,
+                                                                 const int32_t* __restrict__ block_table, int max_pages, int page_size,
+                                                                 TC* __restrict__ pool, TC* __restrict__ q_out, long long ldqo,
+                                                                 int save_here) {
+  extern __shared__ float tile[];  // [rows_per_cta][ch_block]
+  __shared__ const float* src[kConvRows][kConvMaxTaps];
+  __shared__ TC* dst_row[kConvRows];   // the cache row of every row of this CTA
+  const int t0 = blockIdx.x * rows_per_cta, nr = min(rows_per_cta, T - t0);
+  const int c0 = blockIdx.y * ch_block, nc = min(ch_block, ch - c0);
+  const int R = taps - 1;
+  if (threadIdx.x < nr * taps) {
+    const int r = threadIdx.x / taps, j = threadIdx.x - r * taps;
+    const int t = t0 + r, p = pos[t], s = slot[t], back = R - j, sp = p - back;
+    const float* q = nullptr;
+    if (sp >= 0) q = (back == 0 || (t - back >= 0 && slot[t - back] == s)) ? x + (long long)(t - back) * ldx : state + ((long long)s * R + sp % R) * ch;
+    src[r][j] = q;
+  }
+  if (threadIdx.x >= 224 && threadIdx.x - 224 < nr) {
+    const int r = threadIdx.x - 224, p = pos[t0 + r];
+    const int page = block_table[(long long)slot[t0 + r] * max_pages + p / page_size];
+    dst_row[r] = pool + ((long long)page * page_size + p % page_size) * (ch - nq);
+  }
+  __syncthreads();
+  for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) {
+    const int c = c0 + cl;
+    for (int r = 0; r < nr; ++r) {
+      float acc = 0.f;
+#pragma unroll 4
+      for (int j = 0; j < taps; ++j) {
+        const float* q = src[r][j];
+        const float xv = q != nullptr ? q[c] : 0.f;
+        acc = fmaf(ldf(w + (long long)c * taps + j), xv, acc);
+      }
+      tile[r * ch_block + cl] = acc;
+      if (save_here && R > 0) state[((long long)slot[t0 + r] * R + pos[t0 + r] % R) * ch + c] = x[(long long)(t0 + r) * ldx + c];
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int groups = max(0, min(nc, nq + nk - c0)) / group;      // normed groups of this block (blocks are whole groups)
+  for (int rg = warp; rg < nr * groups; rg += nw) {
+    const int r = rg / groups, g = rg - r * groups;
+    float* row = tile + r * ch_block + g * group;
+    const TW* wn = c0 + g * group < nq ? wq : wk;
+    float ss = 0.f;
+    for (int c = lane; c < group; c += 32) ss = fmaf(row[c], row[c], ss);
+    ss = seq_warp_sum(ss);
+    const float f = 1.f / sqrtf(ss / (float)group + eps);
+    for (int c = lane; c < group; c += 32) row[c] = row[c] * f * ldf(wn + c);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < nr * nc; e += blockDim.x) {
+    const int r = e / nc, cl = e - r * nc, c = c0 + cl;
+    const float v = tile[r * ch_block + cl];
+    if (c < nq) stf(q_out + (long long)(t0 + r) * ldqo + c, v);
+    else stf(dst_row[r] + (c - nq), v);
+  }
+}
+
 // The last taps - 1 inputs of every request of the step go into its ring (rows that are followed by taps - 1 more rows of the
 // same request are not among them). A launch of its own when a request may have several rows: a row's ring entry is read by
 // CTAs of other rows of the convolution kernel.
@@ -402,6 +470,34 @@ extern "C" int omc_causal_conv(const float* x, long long ldx, int T, int ch, con
   })
   if (taps > 1 && !single_rows) conv_state_save_kernel<<<dim3(T, (ch + 1023) / 1024), 256, 0, st>>>(x, ldx, ch, taps - 1, T, pos, slot, state);
   return check_launch("omc_causal_conv_silu");
+}
+
+extern "C" int omc_conv_qk_norm_kv_store(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps, const int32_t* pos,
+                                         const int32_t* slot, float* state, int nq, int nk, int group, const void* wq, const void* wk,
+                                         float eps, const int32_t* block_table, int max_pages, int page_size, void* pool, void* q_out,
+                                         long long ldqo, int dt, int single_rows, void* stream) {
+  if (x == nullptr || w == nullptr || pos == nullptr || slot == nullptr || wq == nullptr || wk == nullptr || block_table == nullptr ||
+      pool == nullptr || q_out == nullptr || T < 0 || taps < 1 || taps > kConvMaxTaps || (taps > 1 && state == nullptr) || group <= 0 ||
+      nq <= 0 || nk <= 0 || nq % group || nk % group || ch <= nq + nk || page_size <= 0 || max_pages <= 0)
+    return set_error(OMC_ERR_ARG, "omc_conv_qk_norm_kv_store: bad argument");
+  if (T == 0) return OMC_OK;
+  int ch_block = group >= 512 ? group : (512 / group) * group;
+  if (ch_block > ch) ch_block = ch;
+  if ((size_t)ch_block * kConvRows * sizeof(float) > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_conv_qk_norm_kv_store: group too wide for shared memory");
+  const int blocks = (ch + ch_block - 1) / ch_block;
+  if (blocks > 65535) return set_error(OMC_ERR_SHAPE, "omc_conv_qk_norm_kv_store: too many channel blocks");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rows_per_cta = T >= 256 ? kConvRows : 1;
+  const size_t smem = (size_t)ch_block * rows_per_cta * sizeof(float);
+  OMC_DT_SWITCH(w_dt, TW, OMC_DT_SWITCH(dt, TC, {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(conv_qk_norm_store_kernel<TW, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    conv_qk_norm_store_kernel<TW, TC><<<dim3((T + rows_per_cta - 1) / rows_per_cta, blocks), 256, smem, st>>>(
+        x, ldx, T, ch, ch_block, rows_per_cta, static_cast<const TW*>(w), taps, pos, slot, state, nq, nk, group, static_cast<const TW*>(wq),
+        static_cast<const TW*>(wk), eps, block_table, max_pages, page_size, static_cast<TC*>(pool), static_cast<TC*>(q_out), ldqo,
+        single_rows ? 1 : 0);
+  }))
+  if (taps > 1 && !single_rows) conv_state_save_kernel<<<dim3(T, (ch + 1023) / 1024), 256, 0, st>>>(x, ldx, ch, taps - 1, T, pos, slot, state);
+  return check_launch("omc_conv_qk_norm_kv_store");
 }
 
 extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps,

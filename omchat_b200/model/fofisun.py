@@ -209,6 +209,7 @@ class FofisunDecoder(GraphedDecodeMixin):
         self.runs = cfg.layer_runs()    # layer index of every layer run; cache pools and states are per run
         self.tensor_gemm = dtype == torch.bfloat16
         self.tensor_attention = True    # False: the plain attention kernel for every shape (A/B, tests)
+        self.fused_conv_store = True    # False: convolution, query / key norm + cache append as separate launches (A/B, tests)
         self._moe_ws = {}
         self._init_graphs()
 
@@ -241,15 +242,18 @@ class FofisunDecoder(GraphedDecodeMixin):
         H, G, d, dv = m.heads, m.kv_heads, m.dim, m.vdim
         nq, nk, nv = H * 2 * d, G * 2 * d, G * dv
         z = self._linear(xb, mw.w_in, f32)                                    # [T, q | k | v | gate]
-        if mw.conv is not None:
-            y = torch.empty(T, nq + nk + nv, device=dev, dtype=f32)
-            seqlib.causal_conv(z[:, :nq + nk + nv], mw.conv, pos, slot, cache.states[run].get("conv"), y, single_rows=single_rows)
-        else:
-            y = z
         pool = cache.pools[run]
         q = torch.empty(T, nq, device=dev, dtype=self.dtype)
-        seqlib.qk_norm_kv_store(y[:, :nq], mw.q_norm, y[:, nq:nq + nk], mw.k_norm, y[:, nq + nk:nq + nk + nv], self.eps, pos, slot,
-                                cache.block_table, cache.page_size, pool, q, group=d)
+        if mw.conv is not None and self.fused_conv_store:
+            seqlib.conv_qk_norm_kv_store(z, mw.conv, pos, slot, cache.states[run].get("conv"), nq, nk, d, mw.q_norm, mw.k_norm, self.eps,
+                                         cache.block_table, cache.page_size, pool, q, single_rows=single_rows)
+        else:
+            y = z
+            if mw.conv is not None:
+                y = torch.empty(T, nq + nk + nv, device=dev, dtype=f32)
+                seqlib.causal_conv(z[:, :nq + nk + nv], mw.conv, pos, slot, cache.states[run].get("conv"), y, single_rows=single_rows)
+            seqlib.qk_norm_kv_store(y[:, :nq], mw.q_norm, y[:, nq:nq + nk], mw.k_norm, y[:, nq + nk:nq + nk + nv], self.eps, pos, slot,
+                                    cache.block_table, cache.page_size, pool, q, group=d)
         window = m.window if m.window is not None else seqlib.WINDOW_ALL
         att = torch.empty(T, H * 2 * dv, device=dev, dtype=f32)
         if plans is not None and self.tensor_attention and seqlib.window_attn_mma_ok(H, G, d, dv, self.dtype):

@@ -30,6 +30,7 @@ SIGNATURES = {
     "omc_embed_sinusoid": (_I, [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P, _L, _P]),
     "omc_diff_heads_gate": (_I, [_P, _L, _I, _I, _I, _F, _F, _F, _P, _L, _I, _P, _I, _L, _P]),
     "omc_causal_conv": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _F, _I, _P]),
+    "omc_conv_qk_norm_kv_store": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _F, _P, _I, _I, _P, _P, _L, _I, _I, _P]),
     "omc_linear_state_scan": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _P]),
     "omc_map_rows": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _P]),
     "omc_gated_rms_rows": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _L, _I, _P, _I, _L, _P]),
@@ -419,6 +420,26 @@ def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, slot: 
 def causal_conv(x, w, pos, slot, state, y, single_rows: bool = False):
     """The causal convolution alone (no activation, no unit vectors)."""
     return causal_conv_silu(x, w, pos, slot, state, y, single_rows=single_rows, act=CONV_LINEAR)
+
+
+def conv_qk_norm_kv_store(x: torch.Tensor, w: torch.Tensor, pos, slot, state: Optional[torch.Tensor], nq: int, nk: int, group: int,
+                          wq: torch.Tensor, wk: torch.Tensor, eps: float, block_table: torch.Tensor, page_size: int, pool: torch.Tensor,
+                          q_out: torch.Tensor, single_rows: bool = False):
+    """causal_conv (no activation) over x fp32 [T, nq + nk + nv], then qk_norm_kv_store with norms per `group` channels, in one launch:
+    q_out [T, nq] and the cache rows [k | v] receive the results; the convolved rows are never written."""
+    _need_cuda(x, w, pos, slot, state, wq, wk, block_table, pool, q_out)
+    ch, taps = w.shape
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and x.shape[1] >= ch and w.is_contiguous() and q_out.stride(1) == 1
+    assert pos.dtype == torch.int32 and slot.dtype == torch.int32 and block_table.dtype == torch.int32 and block_table.is_contiguous()
+    assert taps == 1 or (state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, ch))
+    assert pool.is_contiguous() and pool.shape[-1] == ch - nq and pool.dtype == q_out.dtype
+    assert wq.dtype == wk.dtype == w.dtype and wq.numel() == group and wk.numel() == group
+    rc = load().omc_conv_qk_norm_kv_store(_ptr(x), x.stride(0), x.shape[0], ch, _ptr(w), _dt(w), taps, _ptr(pos), _ptr(slot), _ptr(state),
+                                          nq, nk, group, _ptr(wq), _ptr(wk), eps, _ptr(block_table), block_table.shape[1], page_size,
+                                          _ptr(pool), _ptr(q_out), q_out.stride(0), _dt(pool), 1 if single_rows else 0, _stream())
+    _check(rc, "omc_conv_qk_norm_kv_store")
+    if taps > 1 and not single_rows:
+        _core.add_launches(1)
 
 
 def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, out: torch.Tensor, row_begin: torch.Tensor,

@@ -206,6 +206,60 @@ def test_group_norm_of_queries_and_keys_and_cache_append(H, G, d, dv, page):
         assert torch.allclose(row[:nk], want_k[i], atol=1e-5, rtol=1e-5) and torch.allclose(row[nk:], y[i, nq + nk:], atol=1e-6)
 
 
+@pytest.mark.parametrize("H,G,d,dv,taps,page,dtype", [(6, 2, 12, 20, 4, 16, torch.float32), (1, 1, 16, 16, 1, 8, torch.float32),
+                                                     (4, 4, 24, 8, 2, 32, torch.bfloat16), (16, 4, 64, 128, 3, 16, torch.bfloat16)])
+def test_convolution_norm_and_append_in_one_launch(H, G, d, dv, taps, page, dtype):
+    """The fused kernel against convolution -> group norm -> append of the plain model, fed in portions (2 and 300 rows: one row and
+    eight rows per CTA), then single rows; the ring carries the last inputs across the steps."""
+    g = torch.Generator().manual_seed(H + taps)
+    T, eps = 330, 1e-5
+    nq, nk, nv = H * 2 * d, G * 2 * d, G * dv
+    ch = nq + nk + nv
+    x = torch.randn(T, ch + 7, generator=g, dtype=F64)              # columns behind the channels belong to somebody else
+    w = torch.randn(ch, taps, generator=g, dtype=F64)
+    wq, wk = torch.randn(d, generator=g, dtype=F64), torch.randn(d, generator=g, dtype=F64)
+    xr, wr = x.to(torch.float32).double(), w.to(dtype).double()     # the values the kernel sees
+    y = O.causal_conv(xr[:, :ch], wr)
+    want_q = (O.unit_rms(y[:, :nq].view(T, H * 2, d), eps) * wq.to(dtype).double()).reshape(T, nq)
+    want_k = (O.unit_rms(y[:, nq:nq + nk].view(T, G * 2, d), eps) * wk.to(dtype).double()).reshape(T, nk)
+    pg = Pages(nk + nv, 2, T, page, dtype)
+    state = torch.full((2, max(taps - 1, 1), ch), float("nan"), device=DEV) if taps > 1 else None
+    q_out = torch.empty(T, nq, device=DEV, dtype=dtype)
+    xd = _dev(x)
+    at = 0
+    for n in [2, 300] + [1] * 28:
+        pos, slot = _i32(list(range(at, at + n))), _i32([1] * n)
+        seqlib.conv_qk_norm_kv_store(xd[at:at + n], _dev(w, dtype), pos, slot, state, nq, nk, d, _dev(wq, dtype), _dev(wk, dtype), eps, pg.table,
+                                     page, pg.pool, q_out[at:at + n], single_rows=n == 1)
+        at += n
+    assert at == T
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    assert torch.allclose(q_out.double().cpu(), want_q, atol=tol, rtol=tol)
+    j = torch.arange(T, device=DEV)
+    rows = pg.pool[pg.table[1].long()[j // page], j % page].double().cpu()
+    assert torch.allclose(rows[:, :nk], want_k, atol=tol, rtol=tol) and torch.allclose(rows[:, nk:], y[:, nq + nk:], atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("M,N,K,batch", [(1, 13, 192, 1), (37, 24, 2048, 1), (9, 64, 256, 3), (300, 1, 45, 1)])
+def test_linear_layer_with_few_outputs(M, N, K, batch):
+    """Routers and gates: a handful of outputs over a long K, rows of strided buffers, a batch of column slices."""
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, batch * K + 3, generator=g, dtype=F64)
+    w = torch.randn(batch, N, K, generator=g, dtype=F64) * K ** -0.5
+    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        xd, wd = _dev(x, dt), _dev(w, dt)
+        out = torch.full((M, batch * N + 1), float("nan"), device=DEV)
+        seqlib.linear(xd, wd, out, M=M, N=N, K=K, ldx=xd.stride(0), sx=K, ldw=K, sw=N * K, ldy=out.stride(0), sy=N, batch=batch, alpha=0.5)
+        for b in range(batch):
+            want = 0.5 * xd[:, b * K:(b + 1) * K].double().cpu() @ wd[b].double().cpu().T
+            assert torch.allclose(out[:, b * N:(b + 1) * N].double().cpu(), want, atol=tol, rtol=tol)
+        assert torch.isnan(out[:, batch * N:]).all()
+        if batch == 1:      # a row's result does not depend on the rows beside it
+            one = torch.empty(1, N, device=DEV)
+            seqlib.linear(xd[M - 1:M], wd[0], one, K=K, alpha=0.5)
+            assert torch.equal(one[0], out[M - 1, :N])
+
+
 def plain_two_map_attention(q, k, v, H, G, d, dv, scale, window, keep, first_pos=0):
     """q [n, H, 2, d] for positions first_pos.., k [L, G, 2, d], v [L, G, dv] -> [n, H, 2, dv] with the oracle's mask, in float64."""
     n, L = q.shape[0], k.shape[0]
@@ -395,6 +449,20 @@ def test_whole_prompt_against_the_plain_model_layer_by_layer(cfgf, dtype):
         assert len(col) == len(want_layers) == len(model.config.layer_runs())
         for r, (a, b) in enumerate(zip(col, want_layers)):
             assert torch.allclose(a.double().cpu(), b, atol=2e-4 * float(b.abs().max()), rtol=0), f"layer run {r}"
+
+
+def test_fused_and_separate_convolution_paths_agree_in_the_model():
+    cd = config_a()
+    model, sd = build(cd, torch.float32, seed=3)
+    toks = tokens_for(cd, 70, 6)
+    outs = []
+    for fused in (True, False):
+        model.decoder.fused_conv_store = fused
+        steps = [([("a", toks[:40], list(range(40)))], [])] + [([("a", [t], [0])], []) for t in toks[40:]]
+        out, _ = run_schedule(model, steps, 128)
+        outs.append(torch.stack(out["a"]))
+    assert rel_err(outs[0], outs[1].double()) < 1e-5
+    assert close(outs[0], O.forward(sd, cd, toks), torch.float32)
 
 
 def test_plain_and_tensor_core_attention_agree_in_the_model():
