@@ -86,45 +86,79 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
 }
 
 // ---- a few outputs per row (routers, gates, low-rank factors): the tile kernels would leave such a product to a handful of CTAs
-// that each walk all of K. Here a CTA takes 8 rows, holds them in shared memory as fp32, and every warp owns one output column at a
-// time: it reads that row of W once and feeds 8 accumulators, the lanes striding K; a shuffle tree finishes the sums. The order of
-// a sum depends on K alone.
+// that each walk all of K. Here a CTA takes 8 rows, holds them in shared memory as fp32, and each of its 8 warps owns ONE output
+// column (blockIdx.y walks the columns eight at a time): it reads that row of W once and feeds 8 accumulators. A lane takes four
+// consecutive k at a time (one 8- or 16-byte load of W, float4 reads of the rows), the warp strides K by 128, and a shuffle tree
+// finishes the sums - the order of a sum depends on K alone, with or without the vector loads.
 constexpr int kNarrowRows = 8, kNarrowMaxN = 64, kNarrowMaxK = 6144;
 
-template <typename TX, typename TW, typename TY>
+__device__ __forceinline__ void nld4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+}
+__device__ __forceinline__ void nld4(const bf16_t* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x)), hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+  v[0] = lo.x, v[1] = lo.y, v[2] = hi.x, v[3] = hi.y;
+}
+
+template <typename TX, typename TW, typename TY, bool VEC>
 __global__ void __launch_bounds__(256) linear_narrow_kernel(LinearArgs a) {
-  extern __shared__ float nxs[];   // [kNarrowRows][K]
+  extern __shared__ __align__(16) float nxs[];   // [kNarrowRows][KP], KP = K rounded up to 4, the tail zero
   const int m0 = blockIdx.x * kNarrowRows, nr = min(kNarrowRows, a.M - m0);
   const TX* X = static_cast<const TX*>(a.X) + (long long)blockIdx.z * a.sx;
   const TW* W = static_cast<const TW*>(a.W) + (long long)blockIdx.z * a.sw;
   TY* Y = static_cast<TY*>(a.Y) + (long long)blockIdx.z * a.sy;
-  const int K = a.K;
-  for (int e = threadIdx.x; e < kNarrowRows * K; e += blockDim.x) {
-    const int r = e / K, k = e - r * K;
-    nxs[e] = r < nr ? ldf(X + (long long)(m0 + r) * a.ldx + k) : 0.f;
+  const int K = a.K, KP = (K + 3) & ~3;
+  if (VEC) {
+    const int k4n = KP >> 2;
+    for (int e = threadIdx.x; e < kNarrowRows * k4n; e += blockDim.x) {
+      const int r = e / k4n, k = (e - r * k4n) << 2;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (r < nr) nld4(X + (long long)(m0 + r) * a.ldx + k, v);
+      *reinterpret_cast<float4*>(nxs + r * KP + k) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  } else {
+    for (int e = threadIdx.x; e < kNarrowRows * KP; e += blockDim.x) {
+      const int r = e / KP, k = e - r * KP;
+      nxs[e] = (r < nr && k < K) ? ldf(X + (long long)(m0 + r) * a.ldx + k) : 0.f;
+    }
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int n = warp; n < a.N; n += 8) {
-    const TW* wr = W + (long long)n * a.ldw;
-    float acc[kNarrowRows];
+  const int n = blockIdx.y * 8 + warp;
+  if (n >= a.N) return;
+  const TW* wr = W + (long long)n * a.ldw;
+  float acc[kNarrowRows];
 #pragma unroll
-    for (int r = 0; r < kNarrowRows; ++r) acc[r] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const float wv = ldf(wr + k);
+  for (int r = 0; r < kNarrowRows; ++r) acc[r] = 0.f;
+#pragma unroll 4
+  for (int k = lane * 4; k < KP; k += 128) {
+    float wv[4];
+    if (VEC) {
+      nld4(wr + k, wv);
+    } else {
 #pragma unroll
-      for (int r = 0; r < kNarrowRows; ++r) acc[r] = fmaf(nxs[r * K + k], wv, acc[r]);
+      for (int j = 0; j < 4; ++j) wv[j] = k + j < K ? ldf(wr + k + j) : 0.f;
     }
-    float mine = 0.f;
 #pragma unroll
     for (int r = 0; r < kNarrowRows; ++r) {
-      const float v = seq_warp_sum(acc[r]);
-      if (lane == r) mine = v;
+      const float4 xv = *reinterpret_cast<const float4*>(nxs + r * KP + k);
+      acc[r] = fmaf(xv.x, wv[0], acc[r]);
+      acc[r] = fmaf(xv.y, wv[1], acc[r]);
+      acc[r] = fmaf(xv.z, wv[2], acc[r]);
+      acc[r] = fmaf(xv.w, wv[3], acc[r]);
     }
-    if (lane < nr) {
-      const float b = a.bias != nullptr ? ldf(static_cast<const TW*>(a.bias) + blockIdx.z * a.sbias + n) : 0.f;
-      stf(Y + (long long)(m0 + lane) * a.ldy + n, apply_act(mine * a.alpha + b, a.act));
-    }
+  }
+  float mine = 0.f;
+#pragma unroll
+  for (int r = 0; r < kNarrowRows; ++r) {
+    const float v = seq_warp_sum(acc[r]);
+    if (lane == r) mine = v;
+  }
+  if (lane < nr) {
+    const float b = a.bias != nullptr ? ldf(static_cast<const TW*>(a.bias) + blockIdx.z * a.sbias + n) : 0.f;
+    stf(Y + (long long)(m0 + lane) * a.ldy + n, apply_act(mine * a.alpha + b, a.act));
   }
 }
 
@@ -241,15 +275,19 @@ static int launch_linear_mma(const LinearArgs& a, int y_dt, int batch, cudaStrea
 
 template <typename TX, typename TW, typename TY>
 static int launch_narrow_typed(const LinearArgs& a, int batch, cudaStream_t st) {
-  const size_t smem = sizeof(float) * kNarrowRows * (size_t)a.K;
-  if (smem > 48 * 1024) {
-    static bool attr_done[kMaxDevices] = {};
-    if (!attr_done[cur_device()]) {
-      cudaFuncSetAttribute(linear_narrow_kernel<TX, TW, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * kNarrowRows * kNarrowMaxK));
-      attr_done[cur_device()] = true;
-    }
+  const size_t smem = sizeof(float) * kNarrowRows * (size_t)((a.K + 3) & ~3);
+  // vector loads: rows of X and W that start on 8-byte (bf16) / 16-byte (fp32) boundaries and a K that is a multiple of four
+  const bool vec = a.K % 4 == 0 && a.ldx % 4 == 0 && a.ldw % 4 == 0 && a.sx % 4 == 0 && a.sw % 4 == 0 &&
+                   reinterpret_cast<uintptr_t>(a.X) % (4 * sizeof(TX)) == 0 && reinterpret_cast<uintptr_t>(a.W) % (4 * sizeof(TW)) == 0;
+  static bool attr_done[kMaxDevices] = {};
+  if (!attr_done[cur_device()]) {
+    cudaFuncSetAttribute(linear_narrow_kernel<TX, TW, TY, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * kNarrowRows * kNarrowMaxK));
+    cudaFuncSetAttribute(linear_narrow_kernel<TX, TW, TY, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * kNarrowRows * kNarrowMaxK));
+    attr_done[cur_device()] = true;
   }
-  linear_narrow_kernel<TX, TW, TY><<<dim3((a.M + kNarrowRows - 1) / kNarrowRows, 1, batch), 256, smem, st>>>(a);
+  const dim3 grid((a.M + kNarrowRows - 1) / kNarrowRows, (a.N + 7) / 8, batch);
+  if (vec) linear_narrow_kernel<TX, TW, TY, true><<<grid, 256, smem, st>>>(a);
+  else linear_narrow_kernel<TX, TW, TY, false><<<grid, 256, smem, st>>>(a);
   return check_launch("omc_linear");
 }
 

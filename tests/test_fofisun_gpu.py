@@ -68,6 +68,15 @@ def config_c(page=16):
                 attention(8, 1, 16, 64, 9, 2, 2, moe(6, 2, 32, 1.5, 32, 1.0))]}
 
 
+def config_d(page=64):
+    """Matrices large enough for the tensor-core GEMMs (erf-gelu epilogue, skinny decode GEMM, grouped expert GEMM over 128-row
+    tiles) and head shapes of the tensor-core attention."""
+    return {"architecture": "Fofisun", "vocab": 520, "width": 384, "norm": {"eps": 1e-6}, "kv_page_size": page,
+            "loop": {"start": 1, "stop": 2, "times": 2}, "layers": [
+                attention(4, 2, 32, 48, 50, 4, 3, dense(3328)),
+                attention(6, 2, 64, 64, 120, 10, 4, moe(4, 2, 768, 3.0, 512, 2.0))]}
+
+
 def build(cfg_dict, dtype, seed=0, edit=None):
     cfg = FofisunConfig.from_dict(cfg_dict)
     sd = random_state_dict(cfg, seed=seed)
@@ -449,6 +458,62 @@ def test_whole_prompt_against_the_plain_model_layer_by_layer(cfgf, dtype):
         assert len(col) == len(want_layers) == len(model.config.layer_runs())
         for r, (a, b) in enumerate(zip(col, want_layers)):
             assert torch.allclose(a.double().cpu(), b, atol=2e-4 * float(b.abs().max()), rtol=0), f"layer run {r}"
+
+
+def test_wide_layers_on_the_tensor_core_gemms():
+    cd = config_d()
+    model, sd = build(cd, torch.bfloat16, seed=21)
+    toks = tokens_for(cd, 200, 22)
+    want = O.forward(sd, cd, toks)
+    # a long portion (tensor-core GEMMs with 128-row tiles), a short one, then single tokens (skinny GEMMs, graph replay)
+    steps = [([("w", toks[:150], list(range(150)))], []), ([("w", toks[150:170], list(range(20)))], [])]
+    steps += [([("w", [t], [0])], []) for t in toks[170:]]
+    out, _ = run_schedule(model, steps, 256)
+    got = torch.stack(out["w"])
+    assert close(got, want, torch.bfloat16), row_errors(got, want).max()
+
+
+def test_trace_replay_from_a_checkpoint_folder(tmp_path):
+    """The command-line runner on a saved checkpoint: the model class comes from config.json, steps arrive on standard input,
+    logits leave as files; requests pause, end and hand their slots and pages on."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import numpy as np
+    from omchat_b200.model.checkpoint import save_checkpoint
+    cd = config_a(page=64)
+    del cd["kv_page_size"]
+    cfg = FofisunConfig.from_dict(cd)
+    sd = random_state_dict(cfg, seed=23)
+    save_checkpoint(sd, cfg, str(tmp_path / "model"))
+    toks = {k: tokens_for(cd, n, 40 + n) for k, n in (("x", 90), ("y", 70), ("z", 30), ("u", 65), ("v", 5))}
+    plan = [[("x", 50), ("y", 3)], [("x", 1), ("y", 60)], [("y", 7), ("z", 30)], [("x", 39), ("u", 2), ("v", 5)], [("u", 63)]]
+    fed, lines, rows = {k: 0 for k in toks}, [], []
+    for n, step in enumerate(plan):
+        entries, end = [], []
+        for k, c in step:
+            want = [c - 1] if c > 1 else [0]
+            entries.append({"id": k, "tokens": toks[k][fed[k]:fed[k] + c], "want": want})
+            rows.append((n, k, fed[k] + want[0]))
+            fed[k] += c
+            if fed[k] == len(toks[k]):
+                end.append(k)
+        lines.append(json.dumps({"step": n, "entries": entries, "end": end}))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    # four slots, and pages for three requests of two pages each: the later requests take over what the earlier ones give back
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path / "model"), "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "384"], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {n}" for n in range(len(plan))]
+    want = {k: O.forward(sd, cd, toks[k]) for k in toks}
+    at = {}
+    for n, k, p in rows:
+        data = np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, cd["vocab"])
+        i = at.get(n, 0)
+        at[n] = i + 1
+        assert rel_err(torch.from_numpy(data[i:i + 1].copy()), want[k][p:p + 1]) < TOL[torch.float32], (n, k, p)
 
 
 def test_fused_and_separate_convolution_paths_agree_in_the_model():
