@@ -193,6 +193,7 @@ struct WinMmaArgs {
   long long ldo;
   int max_pages, page_size, H, G, d, dv, window, maps, keep_first;
   float scale, softcap;
+  int q_rows;             // rows of the query tile held in shared memory: 64, or the next multiple of 16 above H / G when every item is one token
   int bias_in_smem;       // the bias columns of this key/value head's query heads are staged in shared memory ([window][H / G])
 };
 
@@ -201,7 +202,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   extern __shared__ __align__(16) unsigned char wsm_raw[];
   const int d = a.d, dv = a.dv, pq = d + 8, pv = dv + 8;
   bf16_t* Qs = reinterpret_cast<bf16_t*>(wsm_raw);
-  bf16_t* Ks = Qs + kWmRows * pq;          // [2][64][pq]
+  bf16_t* Ks = Qs + a.q_rows * pq;         // [2][64][pq]
   bf16_t* Vs = Ks + 2 * kWmKeys * pq;      // [2][64][pv]
   float* sbias = reinterpret_cast<float*>(Vs + 2 * kWmKeys * pv);   // [window][rep] when bias_in_smem
   int first_row, n_tok, slot, first_pos;
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int qchunks = d >> 3, vchunks = dv >> 3;
-  for (int i = tid; i < kWmRows * qchunks; i += blockDim.x) {
+  for (int i = tid; i < a.q_rows * qchunks; i += blockDim.x) {
     const int row = i / qchunks, c = i - row * qchunks;
     bf16_t* dst = Qs + row * pq + c * 8;
     if (row < n_rows) w_cp_async16(wsmem_u32(dst), a.q + (long long)(first_row + row / rep) * a.ldq + ((kvh * rep + row % rep) * a.maps + mp) * d + c * 8);
@@ -239,18 +240,21 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   // two threads per key: one page lookup per thread and tile, then 16-byte copies at a constant stride
   auto stage = [&](int buf, int tile) {
     const int j0 = tile < kept_tiles ? tile * kWmKeys : k_begin + (tile - kept_tiles) * kWmKeys, j_end = tile < kept_tiles ? kept_end : k_end;
-    const int key = tid >> 1, half = tid & 1, j = j0 + key;
-    bf16_t* kd = Ks + (buf * kWmKeys + key) * pq;
-    bf16_t* vd = Vs + (buf * kWmKeys + key) * pv;
-    if (j < j_end) {
-      const bf16_t* row = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * roww;
-      const bf16_t* ks = row + (kvh * a.maps + mp) * d;
-      const bf16_t* vs = row + a.G * a.maps * d + kvh * dv;
-      for (int c = half; c < qchunks; c += 2) w_cp_async16(wsmem_u32(kd + c * 8), ks + c * 8);
-      for (int c = half; c < vchunks; c += 2) w_cp_async16(wsmem_u32(vd + c * 8), vs + c * 8);
-    } else {
-      for (int c = half; c < qchunks; c += 2) *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0, 0, 0, 0);
-      for (int c = half; c < vchunks; c += 2) *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0, 0, 0, 0);
+    const int half = tid & 1;
+    for (int key = tid >> 1; key < kWmKeys; key += blockDim.x >> 1) {   // one pass with 128 threads, two with the 64 of a one-token item
+      const int j = j0 + key;
+      bf16_t* kd = Ks + (buf * kWmKeys + key) * pq;
+      bf16_t* vd = Vs + (buf * kWmKeys + key) * pv;
+      if (j < j_end) {
+        const bf16_t* row = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * roww;
+        const bf16_t* ks = row + (kvh * a.maps + mp) * d;
+        const bf16_t* vs = row + a.G * a.maps * d + kvh * dv;
+        for (int c = half; c < qchunks; c += 2) w_cp_async16(wsmem_u32(kd + c * 8), ks + c * 8);
+        for (int c = half; c < vchunks; c += 2) w_cp_async16(wsmem_u32(vd + c * 8), vs + c * 8);
+      } else {
+        for (int c = half; c < qchunks; c += 2) *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0, 0, 0, 0);
+        for (int c = half; c < vchunks; c += 2) *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0, 0, 0, 0);
+      }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -483,15 +487,19 @@ extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, i
   if (n == 0) return OMC_OK;
   if ((long long)G * maps > 65535) return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: more than 65535 key/value heads");
   WinMmaArgs a{static_cast<const bf16_t*>(q), ldq, static_cast<const bf16_t*>(pool), block_table, items, pos, slot, dist_bias, out, ldo,
-               max_pages, page_size, H, G, d, dv, window, maps, keep_first, scale, softcap, 0};
+               max_pages, page_size, H, G, d, dv, window, maps, keep_first, scale, softcap, kWmRows, 0};
+  if (items == nullptr) a.q_rows = ((H / G + 15) / 16) * 16;   // one token per item: only H / G rows exist, and a smaller tile lets more CTAs share an SM
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  size_t smem = sizeof(bf16_t) * ((size_t)kWmRows * (d + 8) + 2 * (size_t)kWmKeys * (d + 8) + 2 * (size_t)kWmKeys * (dv + 8));
+  size_t smem = sizeof(bf16_t) * ((size_t)a.q_rows * (d + 8) + 2 * (size_t)kWmKeys * (d + 8) + 2 * (size_t)kWmKeys * (dv + 8));
   const size_t bias_bytes = sizeof(float) * (size_t)window * (H / G);
   if (dist_bias != nullptr && bias_bytes <= 64 * 1024) {
     a.bias_in_smem = 1;
     smem += bias_bytes;
   }
   dim3 grid(n, G * maps);
+  // one token per item and at most 16 rows: one warp computes, a second helps staging - half the registers per CTA, so that
+  // (with the smaller query tile) four CTAs share an SM instead of three
+  const int threads = a.q_rows == 16 ? 64 : 128;
 #define OMC_WIN_LAUNCH(NV, TO)                                                                                      \
   do {                                                                                                              \
     static bool attr_done[kMaxDevices] = {};                                                                        \
@@ -499,7 +507,7 @@ extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, i
       cudaFuncSetAttribute(window_attn_mma_kernel<NV, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
       attr_done[cur_device()] = true;                                                                               \
     }                                                                                                               \
-    window_attn_mma_kernel<NV, TO><<<grid, 128, smem, st>>>(a);                                                     \
+    window_attn_mma_kernel<NV, TO><<<grid, threads, smem, st>>>(a);                                                     \
   } while (0)
   if (out_dt == OMC_DT_BF16) {
     if (dv <= 64) OMC_WIN_LAUNCH(8, bf16_t);
