@@ -86,11 +86,13 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(LinearArgs a) {
 }
 
 // ---- a few outputs per row (routers, gates, low-rank factors): the tile kernels would leave such a product to a handful of CTAs
-// that each walk all of K. Here a CTA takes 8 rows, holds them in shared memory as fp32, and each of its 8 warps owns ONE output
-// column (blockIdx.y walks the columns eight at a time): it reads that row of W once and feeds 8 accumulators. A lane takes four
-// consecutive k at a time (one 8- or 16-byte load of W, float4 reads of the rows), the warp strides K by 128, and a shuffle tree
-// finishes the sums - the order of a sum depends on K alone, with or without the vector loads.
-constexpr int kNarrowRows = 8, kNarrowMaxN = 64, kNarrowMaxK = 6144;
+// that each walk all of K. Here a CTA takes 8 rows and walks K in chunks of 1024 that it holds in shared memory as fp32; a warp owns
+// up to 8 output columns (n = blockIdx.y * 8 + warp, then in strides of 8 * gridDim.y) with 8 accumulators each: it reads a chunk of
+// that row of W once for all 8 rows. A lane takes four consecutive k at a time (one 8- or 16-byte load of W, float4 reads of the
+// rows), the warp strides the chunk by 128, and a shuffle tree finishes the sums - the order of a sum depends on K alone, with or
+// without the vector loads and however the columns are spread over CTAs (all columns in one CTA for long steps, eight per CTA for
+// steps of a few rows, where there are few row blocks to fill the device with).
+constexpr int kNarrowRows = 8, kNarrowMaxN = 64, kNarrowKC = 1024, kNarrowPerWarp = kNarrowMaxN / 8;
 
 __device__ __forceinline__ void nld4(const float* p, float (&v)[4]) {
   const float4 t = *reinterpret_cast<const float4*>(p);
@@ -103,62 +105,77 @@ __device__ __forceinline__ void nld4(const bf16_t* p, float (&v)[4]) {
 }
 
 template <typename TX, typename TW, typename TY, bool VEC>
-__global__ void __launch_bounds__(256) linear_narrow_kernel(LinearArgs a) {
-  extern __shared__ __align__(16) float nxs[];   // [kNarrowRows][KP], KP = K rounded up to 4, the tail zero
+__global__ void __launch_bounds__(256, 2) linear_narrow_kernel(LinearArgs a) {
+  __shared__ __align__(16) float nxs[kNarrowRows][kNarrowKC];
   const int m0 = blockIdx.x * kNarrowRows, nr = min(kNarrowRows, a.M - m0);
   const TX* X = static_cast<const TX*>(a.X) + (long long)blockIdx.z * a.sx;
   const TW* W = static_cast<const TW*>(a.W) + (long long)blockIdx.z * a.sw;
   TY* Y = static_cast<TY*>(a.Y) + (long long)blockIdx.z * a.sy;
-  const int K = a.K, KP = (K + 3) & ~3;
-  if (VEC) {
-    const int k4n = KP >> 2;
-    for (int e = threadIdx.x; e < kNarrowRows * k4n; e += blockDim.x) {
-      const int r = e / k4n, k = (e - r * k4n) << 2;
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (r < nr) nld4(X + (long long)(m0 + r) * a.ldx + k, v);
-      *reinterpret_cast<float4*>(nxs + r * KP + k) = make_float4(v[0], v[1], v[2], v[3]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.y * 8 + warp, stride = 8 * gridDim.y;
+  float acc[kNarrowPerWarp][kNarrowRows];
+#pragma unroll
+  for (int i = 0; i < kNarrowPerWarp; ++i)
+#pragma unroll
+    for (int r = 0; r < kNarrowRows; ++r) acc[i][r] = 0.f;
+  for (int kc = 0; kc < a.K; kc += kNarrowKC) {
+    const int kn = min(kNarrowKC, a.K - kc), knp = (kn + 3) & ~3;   // the chunk's columns, rounded up to 4 with a zero tail
+    if (kc > 0) __syncthreads();
+    if (VEC) {
+      const int k4n = knp >> 2;
+      for (int e = threadIdx.x; e < kNarrowRows * k4n; e += blockDim.x) {
+        const int r = e / k4n, k = (e - r * k4n) << 2;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r < nr) nld4(X + (long long)(m0 + r) * a.ldx + kc + k, v);
+        *reinterpret_cast<float4*>(&nxs[r][k]) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    } else {
+      for (int e = threadIdx.x; e < kNarrowRows * knp; e += blockDim.x) {
+        const int r = e / knp, k = e - r * knp;
+        nxs[r][k] = (r < nr && k < kn) ? ldf(X + (long long)(m0 + r) * a.ldx + kc + k) : 0.f;
+      }
     }
-  } else {
-    for (int e = threadIdx.x; e < kNarrowRows * KP; e += blockDim.x) {
-      const int r = e / KP, k = e - r * KP;
-      nxs[e] = (r < nr && k < K) ? ldf(X + (long long)(m0 + r) * a.ldx + k) : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kNarrowPerWarp; ++i) {
+      const int n = n0 + i * stride;
+      if (n < a.N) {
+        const TW* wr = W + (long long)n * a.ldw + kc;
+#pragma unroll 2
+        for (int k = lane * 4; k < knp; k += 128) {
+          float wv[4];
+          if (VEC) {
+            nld4(wr + k, wv);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = k + j < kn ? ldf(wr + k + j) : 0.f;
+          }
+#pragma unroll
+          for (int r = 0; r < kNarrowRows; ++r) {
+            const float4 xv = *reinterpret_cast<const float4*>(&nxs[r][k]);
+            acc[i][r] = fmaf(xv.x, wv[0], acc[i][r]);
+            acc[i][r] = fmaf(xv.y, wv[1], acc[i][r]);
+            acc[i][r] = fmaf(xv.z, wv[2], acc[i][r]);
+            acc[i][r] = fmaf(xv.w, wv[3], acc[i][r]);
+          }
+        }
+      }
     }
   }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.y * 8 + warp;
-  if (n >= a.N) return;
-  const TW* wr = W + (long long)n * a.ldw;
-  float acc[kNarrowRows];
 #pragma unroll
-  for (int r = 0; r < kNarrowRows; ++r) acc[r] = 0.f;
-#pragma unroll 4
-  for (int k = lane * 4; k < KP; k += 128) {
-    float wv[4];
-    if (VEC) {
-      nld4(wr + k, wv);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) wv[j] = k + j < K ? ldf(wr + k + j) : 0.f;
-    }
+  for (int i = 0; i < kNarrowPerWarp; ++i) {
+    const int n = n0 + i * stride;
+    if (n >= a.N) break;
+    float mine = 0.f;
 #pragma unroll
     for (int r = 0; r < kNarrowRows; ++r) {
-      const float4 xv = *reinterpret_cast<const float4*>(nxs + r * KP + k);
-      acc[r] = fmaf(xv.x, wv[0], acc[r]);
-      acc[r] = fmaf(xv.y, wv[1], acc[r]);
-      acc[r] = fmaf(xv.z, wv[2], acc[r]);
-      acc[r] = fmaf(xv.w, wv[3], acc[r]);
+      const float v = seq_warp_sum(acc[i][r]);
+      if (lane == r) mine = v;
     }
-  }
-  float mine = 0.f;
-#pragma unroll
-  for (int r = 0; r < kNarrowRows; ++r) {
-    const float v = seq_warp_sum(acc[r]);
-    if (lane == r) mine = v;
-  }
-  if (lane < nr) {
-    const float b = a.bias != nullptr ? ldf(static_cast<const TW*>(a.bias) + blockIdx.z * a.sbias + n) : 0.f;
-    stf(Y + (long long)(m0 + lane) * a.ldy + n, apply_act(mine * a.alpha + b, a.act));
+    if (lane < nr) {
+      const float b = a.bias != nullptr ? ldf(static_cast<const TW*>(a.bias) + blockIdx.z * a.sbias + n) : 0.f;
+      stf(Y + (long long)(m0 + lane) * a.ldy + n, apply_act(mine * a.alpha + b, a.act));
+    }
   }
 }
 
@@ -275,19 +292,13 @@ static int launch_linear_mma(const LinearArgs& a, int y_dt, int batch, cudaStrea
 
 template <typename TX, typename TW, typename TY>
 static int launch_narrow_typed(const LinearArgs& a, int batch, cudaStream_t st) {
-  const size_t smem = sizeof(float) * kNarrowRows * (size_t)((a.K + 3) & ~3);
   // vector loads: rows of X and W that start on 8-byte (bf16) / 16-byte (fp32) boundaries and a K that is a multiple of four
   const bool vec = a.K % 4 == 0 && a.ldx % 4 == 0 && a.ldw % 4 == 0 && a.sx % 4 == 0 && a.sw % 4 == 0 &&
                    reinterpret_cast<uintptr_t>(a.X) % (4 * sizeof(TX)) == 0 && reinterpret_cast<uintptr_t>(a.W) % (4 * sizeof(TW)) == 0;
-  static bool attr_done[kMaxDevices] = {};
-  if (!attr_done[cur_device()]) {
-    cudaFuncSetAttribute(linear_narrow_kernel<TX, TW, TY, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * kNarrowRows * kNarrowMaxK));
-    cudaFuncSetAttribute(linear_narrow_kernel<TX, TW, TY, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * kNarrowRows * kNarrowMaxK));
-    attr_done[cur_device()] = true;
-  }
-  const dim3 grid((a.M + kNarrowRows - 1) / kNarrowRows, (a.N + 7) / 8, batch);
-  if (vec) linear_narrow_kernel<TX, TW, TY, true><<<grid, 256, smem, st>>>(a);
-  else linear_narrow_kernel<TX, TW, TY, false><<<grid, 256, smem, st>>>(a);
+  // where the columns run is a matter of occupancy only: every column is summed by one warp in the same order either way
+  const dim3 grid((a.M + kNarrowRows - 1) / kNarrowRows, a.M <= 64 ? (a.N + 7) / 8 : 1, batch);
+  if (vec) linear_narrow_kernel<TX, TW, TY, true><<<grid, 256, 0, st>>>(a);
+  else linear_narrow_kernel<TX, TW, TY, false><<<grid, 256, 0, st>>>(a);
   return check_launch("omc_linear");
 }
 
@@ -301,7 +312,7 @@ static int launch_narrow(const LinearArgs& a, int y_dt, int batch, cudaStream_t 
 template <typename TX, typename TW>
 static int launch_linear(const LinearArgs& a, int y_dt, int batch, cudaStream_t st) {
   // few outputs over a long K: the choice depends on widths only, never on M
-  if (a.tile_group == nullptr && a.N <= kNarrowMaxN && a.K <= kNarrowMaxK && a.K >= 4 * a.N) return launch_narrow<TX, TW>(a, y_dt, batch, st);
+  if (a.tile_group == nullptr && a.N <= kNarrowMaxN && a.K >= 4 * a.N) return launch_narrow<TX, TW>(a, y_dt, batch, st);
   dim3 grid((a.N + kLinBN - 1) / kLinBN, (a.M + kLinBM - 1) / kLinBM, batch);
   if (y_dt == OMC_DT_F32) linear_tile_kernel<TX, TW, float><<<grid, 256, 0, st>>>(a);
   else if (y_dt == OMC_DT_BF16) linear_tile_kernel<TX, TW, bf16_t><<<grid, 256, 0, st>>>(a);
@@ -329,7 +340,7 @@ extern "C" int omc_linear_bias(const void* X, int x_dt, long long ldx, long long
   if (x_dt == OMC_DT_F32 && w_dt == OMC_DT_BF16) return launch_linear<float, bf16_t>(a, y_dt, batch, st);
   if (x_dt == OMC_DT_BF16 && w_dt == OMC_DT_BF16) {
     // the choice depends on layout and widths only, never on M: a row is computed by the same kernel in every batch
-    const bool narrow = tile_group == nullptr && N <= kNarrowMaxN && K <= kNarrowMaxK && K >= 4 * N;
+    const bool narrow = tile_group == nullptr && N <= kNarrowMaxN && K >= 4 * N;
     if (!narrow && mma_operands_ok(a) && (long long)N * K >= 4096) return launch_linear_mma(a, y_dt, batch, st);
     return launch_linear<bf16_t, bf16_t>(a, y_dt, batch, st);
   }

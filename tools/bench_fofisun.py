@@ -11,6 +11,7 @@ shapes against their rooflines, each beside the like kernel of the Tifisun path:
   omc_window_attn_mma, two maps + kept keys   prefill: FLOPs = rows x visible keys x heads x maps x 2 (dim + vdim) against the measured
                                               bf16 peak; decode: bytes of the visible keys and values against the copy bandwidth.
                                               Like kernel: the same entry with one map and no kept keys at equal head widths.
+  omc_conv_qk_norm_kv_store (the two below in one launch), omc_linear with a few outputs (the router),
   omc_causal_conv (linear), omc_qk_norm_kv_store (per group), omc_diff_heads_gate, omc_glu_mul (clamped), omc_embed_sinusoid,
   omc_moe_combine_norm (with the next norm): bytes read + written against the copy bandwidth; like kernels: omc_causal_conv_silu,
   omc_qk_norm_kv_store (whole projection), omc_gated_rms_rows, omc_glu_mul (gelu), omc_embed_scale, omc_post_norm_residual.
@@ -126,6 +127,18 @@ def kernels(z, n_seq, L, B, ctx):
     out["qk_group_norm_kv_store"] = rate(ms, nbytes)
     ms = timed(lambda: seqlib.qk_norm_kv_store(yz[:, :nq], wq, yz[:, nq:nq + nk], wk, yz[:, nq + nk:], 1e-5, pos, slot, table, page, pool, qo))
     out["tifisun_qk_norm_kv_store"] = rate(ms, nbytes)
+    ms_sep = out["causal_conv_linear"]["ms"] + out["qk_group_norm_kv_store"]["ms"]
+    ms = timed(lambda: seqlib.conv_qk_norm_kv_store(xz, cw, pos, slot, cst, nq, nk, d, wd, wd, 1e-5, table, page, pool, qo))
+    out["conv_qk_norm_kv_store_fused"] = rate(ms, T * ch * (4 + 2), ms_separate=ms_sep)
+    out["tifisun_conv_then_qk_norm"] = rate(out["tifisun_causal_conv_silu"]["ms"] + out["tifisun_qk_norm_kv_store"]["ms"], T * ch * (4 + 2))
+    # ---- the router's product: a few outputs over the width (rows of the step x router rows + the shared expert's gate row)
+    nr = -(-(z["E"] + 1) // 8) * 8
+    xr, wr, zr = (torch.randn(T, C, device=dev) * 0.5).to(bf), (torch.randn(nr, C, device=dev) * C ** -0.5).to(bf), torch.empty(T, nr, device=dev)
+    ms = timed(lambda: seqlib.linear(xr, wr, zr))
+    out["router_linear_prefill"] = rate(ms, T * C * 2 + T * nr * 4 + nr * C * 2)
+    ms = timed(lambda: seqlib.linear(xr[:B], wr, zr[:B]))
+    out["router_linear_decode"] = rate(ms, B * C * 2 + B * nr * 4 + nr * C * 2, batch=B)
+    del xr, zr
     # ---- differential combine + head norm + gate against the gated RMS norm
     on = torch.empty(T, H * dv, device=dev, dtype=bf)
     gate = xz[:, ch:]
