@@ -237,6 +237,16 @@ int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d
 int omc_diff_heads_gate(const float* a, long long lda, int T, int H, int dv, float lambda, float mult, float eps, const float* gate,
                         long long ldg, int gate_act, void* y, int y_dt, long long ldy, void* stream);
 
+/* Differential attention of prompt portions in one kernel (bf16 q and pool; shapes as omc_window_attn_mma, and both maps' tiles must
+ * fit shared memory - omc_diff_attn_pair_ok says 1): omc_window_attn_mma with two maps, no soft cap and no bias, followed by
+ * omc_diff_heads_gate, with the values of a key tile staged once for both maps and the maps themselves kept in registers.
+ * q [T, H, 2, d], pool rows [G, 2, d | G, dv], items as omc_window_attn_mma (not NULL), gate fp32 [T, ldg] or NULL, out [T, H * dv]. */
+int omc_diff_attn_pair_ok(int H, int G, int d, int dv);
+int omc_diff_attn_pair(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool, const int32_t* block_table,
+                       int max_pages, int page_size, const int32_t* items, int n_items, int window, int keep_first, float scale,
+                       float lambda, float mult, float eps, const float* gate, long long ldg, int gate_act, void* out, int out_dt,
+                       long long ldo, void* stream);
+
 /* In place over x[t, :cols] (fp32): op 1: silu; op 2: x <- exp(-exp(A_log[c / group]) * softplus(x + bias[c])) - the same
  * functions the recurrence applies while staging, as one pass for steps with long portions. */
 int omc_map_rows(float* x, long long ldx, int rows, int cols, int op, const float* A_log, const float* bias, int group, void* stream);

@@ -383,6 +383,239 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// Differential attention of prompt portions in ONE kernel: a CTA takes the 64 (token, query head) rows of one key/value head for BOTH
+// score maps. Every 64-key tile is staged once - the two maps' keys and the values they share - and each warp runs the two maps one
+// after the other on it (S = Q_m K_m^T, mask, online softmax of its own, P_m V into an accumulator set of its own). The epilogue
+// forms o = a1 - lambda a2 on the accumulators, the RMS norm over the head's values (a row's values sit in the four lanes of a
+// quad), the constant factor and the elementwise gate, and writes the mixer's pre-projection rows. Compared with one CTA per map and a
+// combine kernel behind it: the values travel to shared memory once instead of twice, and the two fp32 maps never travel at all.
+struct DiffPairArgs {
+  const bf16_t* q;
+  long long ldq;
+  const bf16_t* pool;
+  const int32_t* bt;
+  const int32_t* items;   // [n][4] (first_row, n_tok, slot, first_pos)
+  const float* gate;      // [T, ldg] or NULL
+  long long ldg;
+  void* out;              // [T, H * dv]
+  long long ldo;
+  int max_pages, page_size, H, G, d, dv, window, keep_first, gate_act;
+  float scale, lambda, mult, eps;
+};
+
+template <int NV, typename TO>
+__global__ void __launch_bounds__(128) diff_attn_pair_kernel(DiffPairArgs a) {
+  extern __shared__ __align__(16) unsigned char wsm_raw[];
+  const int d = a.d, dv = a.dv, pq = d + 8, pv = dv + 8;
+  bf16_t* Qs = reinterpret_cast<bf16_t*>(wsm_raw);   // [2 maps][64][pq]
+  bf16_t* Ks = Qs + 2 * kWmRows * pq;                // [2 buffers][2 maps][64][pq]
+  bf16_t* Vs = Ks + 4 * kWmKeys * pq;                // [2 buffers][64][pv]
+  const int32_t* it = a.items + blockIdx.x * 4;
+  const int first_row = it[0], n_tok = it[1], slot = it[2], first_pos = it[3];
+  const int kvh = blockIdx.y, rep = a.H / a.G, n_rows = n_tok * rep;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int qchunks = d >> 3, vchunks = dv >> 3;
+  for (int i = tid; i < 2 * kWmRows * qchunks; i += blockDim.x) {
+    const int mm = i / (kWmRows * qchunks), r2 = i - mm * kWmRows * qchunks, row = r2 / qchunks, c = r2 - row * qchunks;
+    bf16_t* dst = Qs + (mm * kWmRows + row) * pq + c * 8;
+    if (row < n_rows) w_cp_async16(wsmem_u32(dst), a.q + (long long)(first_row + row / rep) * a.ldq + ((kvh * rep + row % rep) * 2 + mm) * d + c * 8);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+  }
+  const int row0 = warp * 16 + g, row1 = row0 + 8;
+  const int p0 = row0 < n_rows ? first_pos + row0 / rep : -1, p1 = row1 < n_rows ? first_pos + row1 / rep : -1;   // -1: no such row
+  const int h0 = kvh * rep + row0 % rep, h1 = kvh * rep + row1 % rep;
+  const int32_t* bt = a.bt + (long long)slot * a.max_pages;
+  int k_begin = max(0, first_pos - a.window + 1);
+  const int k_end = first_pos + n_tok;
+  int kept_end = min(a.keep_first, k_begin);
+  if (kept_end == k_begin) k_begin = 0, kept_end = 0;
+  const int kept_tiles = (kept_end + kWmKeys - 1) / kWmKeys, n_tiles = kept_tiles + (k_end - k_begin + kWmKeys - 1) / kWmKeys;
+  const int roww = a.G * (2 * d + dv);
+  auto stage = [&](int buf, int tile) {
+    const int j0 = tile < kept_tiles ? tile * kWmKeys : k_begin + (tile - kept_tiles) * kWmKeys, j_end = tile < kept_tiles ? kept_end : k_end;
+    const int key = tid >> 1, half = tid & 1, j = j0 + key;
+    bf16_t* k0d = Ks + ((buf * 2 + 0) * kWmKeys + key) * pq;
+    bf16_t* k1d = Ks + ((buf * 2 + 1) * kWmKeys + key) * pq;
+    bf16_t* vd = Vs + (buf * kWmKeys + key) * pv;
+    if (j < j_end) {
+      const bf16_t* row = a.pool + ((long long)bt[j / a.page_size] * a.page_size + j % a.page_size) * roww;
+      const bf16_t* ks = row + kvh * 2 * d;            // the two maps' keys of this key/value head lie side by side
+      const bf16_t* vs = row + a.G * 2 * d + kvh * dv;
+      for (int c = half; c < qchunks; c += 2) {
+        w_cp_async16(wsmem_u32(k0d + c * 8), ks + c * 8);
+        w_cp_async16(wsmem_u32(k1d + c * 8), ks + d + c * 8);
+      }
+      for (int c = half; c < vchunks; c += 2) w_cp_async16(wsmem_u32(vd + c * 8), vs + c * 8);
+    } else {
+      for (int c = half; c < qchunks; c += 2) {
+        *reinterpret_cast<uint4*>(k0d + c * 8) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(k1d + c * 8) = make_uint4(0, 0, 0, 0);
+      }
+      for (int c = half; c < vchunks; c += 2) *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float m0[2] = {-INFINITY, -INFINITY}, m1[2] = {-INFINITY, -INFINITY}, l0[2] = {0.f, 0.f}, l1[2] = {0.f, 0.f};
+  float o[2][NV][4];
+#pragma unroll
+  for (int mm = 0; mm < 2; ++mm)
+#pragma unroll
+    for (int j = 0; j < NV; ++j) o[mm][j][0] = o[mm][j][1] = o[mm][j][2] = o[mm][j][3] = 0.f;
+  const int nv = dv >> 3;
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float sc2 = a.scale * kLog2e;   // scores in base-2 units
+  stage(0, 0);
+  for (int kt = 0; kt < n_tiles; ++kt) {
+    const int buf = kt & 1;
+    const int j0 = kt < kept_tiles ? kt * kWmKeys : k_begin + (kt - kept_tiles) * kWmKeys, j_end = kt < kept_tiles ? kept_end : k_end;
+    if (kt + 1 < n_tiles) {
+      stage(buf ^ 1, kt + 1);   // released by the barrier that ended the previous tile
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp * 16 < n_rows) {
+      const bf16_t* Vc = Vs + buf * kWmKeys * pv;
+      const uint32_t v_base = wsmem_u32(Vc + ((lane & 7) + 8 * ((lane >> 3) & 1)) * pv + 8 * (lane >> 4));
+#pragma unroll
+      for (int mm = 0; mm < 2; ++mm) {
+        const bf16_t* Kc = Ks + (buf * 2 + mm) * kWmKeys * pq;
+        float s[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        const uint32_t q_base = wsmem_u32(Qs + (mm * kWmRows + warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * pq + 8 * (lane >> 4));
+        const uint32_t k_base = wsmem_u32(Kc + ((lane & 7) + 8 * (lane >> 4)) * pq + 8 * ((lane >> 3) & 1));
+        for (int kk = 0; kk < d; kk += 16) {
+          uint32_t a0, a1, a2, a3;
+          w_ldsm_x4(q_base + kk * 2, a0, a1, a2, a3);
+#pragma unroll
+          for (int n2 = 0; n2 < 4; ++n2) {
+            uint32_t b0, b1, b2, b3;
+            w_ldsm_x4(k_base + (n2 * 16 * pq + kk) * 2, b0, b1, b2, b3);
+            w_mma_bf16(s[2 * n2], a0, a1, a2, a3, b0, b1);
+            w_mma_bf16(s[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
+          }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = j0 + n * 8 + 2 * t4 + (e & 1);
+            const int dist = (e < 2 ? p0 : p1) - key;
+            s[n][e] = (key < j_end && dist >= 0 && (dist < a.window || key < a.keep_first)) ? s[n][e] * sc2 : -INFINITY;
+          }
+          mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+          mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0[mm], mx0), mn1 = fmaxf(m1[mm], mx1);
+        const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;   // rows that see nothing yet
+        const float c0 = exp2f(m0[mm] - ms0), c1 = exp2f(m1[mm] - ms1);
+        m0[mm] = mn0;
+        m1[mm] = mn1;
+        float rs0 = 0.f, rs1 = 0.f;
+        uint32_t p[8][2];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          p[n][0] = w_pack2(exp2f(s[n][0] - ms0), exp2f(s[n][1] - ms0));
+          p[n][1] = w_pack2(exp2f(s[n][2] - ms1), exp2f(s[n][3] - ms1));
+          // the denominator sums the ROUNDED probabilities, the ones the numerator uses
+          const float2 f0 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&p[n][0]));
+          const float2 f1 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&p[n][1]));
+          rs0 += f0.x + f0.y;
+          rs1 += f1.x + f1.y;
+        }
+        l0[mm] = l0[mm] * c0 + rs0;
+        l1[mm] = l1[mm] * c1 + rs1;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          o[mm][j][0] *= c0;
+          o[mm][j][1] *= c0;
+          o[mm][j][2] *= c1;
+          o[mm][j][3] *= c1;
+        }
+#pragma unroll
+        for (int kb16 = 0; kb16 < 4; ++kb16) {
+          const uint32_t a0 = p[2 * kb16][0], a1 = p[2 * kb16][1], a2 = p[2 * kb16 + 1][0], a3 = p[2 * kb16 + 1][1];
+#pragma unroll
+          for (int j = 0; j < NV; j += 2) {
+            if (j < nv) {   // dv is a multiple of 16: tiles come in pairs
+              uint32_t b0, b1, b2, b3;
+              w_ldsm_x4_t(v_base + (kb16 * 16 * pv + j * 8) * 2, b0, b1, b2, b3);
+              w_mma_bf16(o[mm][j], a0, a1, a2, a3, b0, b1);
+              w_mma_bf16(o[mm][j + 1], a0, a1, a2, a3, b2, b3);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();   // every warp is done with this tile's buffers
+  }
+  float i0[2], i1[2];
+#pragma unroll
+  for (int mm = 0; mm < 2; ++mm) {
+    float x = l0[mm], y = l1[mm];
+    x += __shfl_xor_sync(0xffffffffu, x, 1);
+    x += __shfl_xor_sync(0xffffffffu, x, 2);
+    y += __shfl_xor_sync(0xffffffffu, y, 1);
+    y += __shfl_xor_sync(0xffffffffu, y, 2);
+    i0[mm] = 1.f / x;
+    i1[mm] = 1.f / y;
+  }
+  // o = a1 - lambda a2 in place of the first map's accumulators; a row's dv values are spread over the four lanes of its quad
+  float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    if (j < nv) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float v = e < 2 ? o[0][j][e] * i0[0] - a.lambda * (o[1][j][e] * i0[1]) : o[0][j][e] * i1[0] - a.lambda * (o[1][j][e] * i1[1]);
+        o[0][j][e] = v;
+        if (e < 2) ss0 = fmaf(v, v, ss0);
+        else ss1 = fmaf(v, v, ss1);
+      }
+    }
+  }
+  ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1);
+  ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+  ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1);
+  ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+  const float f0 = a.mult / sqrtf(ss0 / (float)dv + a.eps), f1 = a.mult / sqrtf(ss1 / (float)dv + a.eps);
+  const long long t0 = first_row + row0 / rep, t1 = first_row + row1 / rep;
+  TO* out0 = static_cast<TO*>(a.out) + t0 * a.ldo + h0 * dv;
+  TO* out1 = static_cast<TO*>(a.out) + t1 * a.ldo + h1 * dv;
+  auto act = [&](float z) { return a.gate_act == 2 ? 1.f / (1.f + __expf(-z)) : (a.gate_act == 1 ? z / (1.f + __expf(-z)) : z); };
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    if (j < nv) {
+      const int col = j * 8 + 2 * t4;
+      if (row0 < n_rows) {
+        float g0 = 1.f, g1 = 1.f;
+        if (a.gate != nullptr) {
+          const float2 z = *reinterpret_cast<const float2*>(a.gate + t0 * a.ldg + h0 * dv + col);
+          g0 = act(z.x), g1 = act(z.y);
+        }
+        w_st_pair(out0 + col, o[0][j][0] * f0 * g0, o[0][j][1] * f0 * g1);
+      }
+      if (row1 < n_rows) {
+        float g0 = 1.f, g1 = 1.f;
+        if (a.gate != nullptr) {
+          const float2 z = *reinterpret_cast<const float2*>(a.gate + t1 * a.ldg + h1 * dv + col);
+          g0 = act(z.x), g1 = act(z.y);
+        }
+        w_st_pair(out1 + col, o[0][j][2] * f1 * g0, o[0][j][3] * f1 * g1);
+      }
+    }
+  }
+}
+
 // Two score maps of a head -> one output: o = a1 - lambda a2, o / sqrt(mean(o^2) + eps) over the head's dv values, times a constant,
 // times an elementwise gate. One CTA per row, a warp per head.
 template <typename TY>
@@ -520,4 +753,51 @@ extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, i
   }
 #undef OMC_WIN_LAUNCH
   return check_launch("omc_window_attn_mma");
+}
+
+static size_t diff_pair_smem(int d, int dv) {
+  return sizeof(bf16_t) * (2 * (size_t)kWmRows * (d + 8) + 4 * (size_t)kWmKeys * (d + 8) + 2 * (size_t)kWmKeys * (dv + 8));
+}
+
+extern "C" int omc_diff_attn_pair_ok(int H, int G, int d, int dv) {
+  return (omc_window_attn_mma_ok(H, G, d, dv) && diff_pair_smem(d, dv) <= 200 * 1024) ? 1 : 0;
+}
+
+extern "C" int omc_diff_attn_pair(const void* q, long long ldq, int T, int H, int G, int d, int dv, const void* pool,
+                                  const int32_t* block_table, int max_pages, int page_size, const int32_t* items, int n_items, int window,
+                                  int keep_first, float scale, float lambda, float mult, float eps, const float* gate, long long ldg,
+                                  int gate_act, void* out, int out_dt, long long ldo, void* stream) {
+  if (q == nullptr || pool == nullptr || block_table == nullptr || items == nullptr || out == nullptr || T < 0 || n_items < 0 || window < 1 ||
+      keep_first < 0 || page_size <= 0 || max_pages <= 0 || gate_act < 0 || gate_act > 2)
+    return set_error(OMC_ERR_ARG, "omc_diff_attn_pair: bad argument");
+  if (!omc_diff_attn_pair_ok(H, G, d, dv) || ldq % 8 || ldo % 2 || ldg % 2 || reinterpret_cast<uintptr_t>(q) % 16 ||
+      reinterpret_cast<uintptr_t>(pool) % 16 || reinterpret_cast<uintptr_t>(gate) % 8)
+    return set_error(OMC_ERR_SHAPE, "omc_diff_attn_pair: shape or alignment not supported (see omc_diff_attn_pair_ok)");
+  if (n_items == 0) return OMC_OK;
+  if (G > 65535) return set_error(OMC_ERR_SHAPE, "omc_diff_attn_pair: more than 65535 key/value heads");
+  DiffPairArgs a{static_cast<const bf16_t*>(q), ldq, static_cast<const bf16_t*>(pool), block_table, items, gate, ldg, out, ldo,
+                 max_pages, page_size, H, G, d, dv, window, keep_first, gate_act, scale, lambda, mult, eps};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = diff_pair_smem(d, dv);
+  dim3 grid(n_items, G);
+#define OMC_PAIR_LAUNCH(NV, TO)                                                                                    \
+  do {                                                                                                             \
+    static bool attr_done[kMaxDevices] = {};                                                                       \
+    if (!attr_done[cur_device()]) {                                                                                \
+      cudaFuncSetAttribute(diff_attn_pair_kernel<NV, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+      attr_done[cur_device()] = true;                                                                              \
+    }                                                                                                              \
+    diff_attn_pair_kernel<NV, TO><<<grid, 128, smem, st>>>(a);                                                     \
+  } while (0)
+  if (out_dt == OMC_DT_BF16) {
+    if (dv <= 64) OMC_PAIR_LAUNCH(8, bf16_t);
+    else OMC_PAIR_LAUNCH(16, bf16_t);
+  } else if (out_dt == OMC_DT_F32) {
+    if (dv <= 64) OMC_PAIR_LAUNCH(8, float);
+    else OMC_PAIR_LAUNCH(16, float);
+  } else {
+    return set_error(OMC_ERR_ARG, "omc_diff_attn_pair: unknown output dtype");
+  }
+#undef OMC_PAIR_LAUNCH
+  return check_launch("omc_diff_attn_pair");
 }

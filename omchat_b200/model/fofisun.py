@@ -209,6 +209,7 @@ class FofisunDecoder(GraphedDecodeMixin):
         self.runs = cfg.layer_runs()    # layer index of every layer run; cache pools and states are per run
         self.tensor_gemm = dtype == torch.bfloat16
         self.tensor_attention = True    # False: the plain attention kernel for every shape (A/B, tests)
+        self.fused_maps = True          # False: prompt portions run one CTA per score map and the combine kernel behind it (A/B, tests)
         self.fused_conv_store = True    # False: convolution, query / key norm + cache append as separate launches (A/B, tests)
         self._moe_ws = {}
         self._init_graphs()
@@ -255,22 +256,28 @@ class FofisunDecoder(GraphedDecodeMixin):
             seqlib.qk_norm_kv_store(y[:, :nq], mw.q_norm, y[:, nq:nq + nk], mw.k_norm, y[:, nq + nk:nq + nk + nv], self.eps, pos, slot,
                                     cache.block_table, cache.page_size, pool, q, group=d)
         window = m.window if m.window is not None else seqlib.WINDOW_ALL
-        att = torch.empty(T, H * 2 * dv, device=dev, dtype=f32)
-        if plans is not None and self.tensor_attention and seqlib.window_attn_mma_ok(H, G, d, dv, self.dtype):
+        on = torch.empty(T, H * dv, device=dev, dtype=self.dtype)
+        gate = z[:, mw.cols["g"]]
+        tensor = plans is not None and self.tensor_attention and seqlib.window_attn_mma_ok(H, G, d, dv, self.dtype)
+        items = None
+        if tensor and plans["portions"] is not None:
             rep = H // G
-            if plans["portions"] is None:        # one row per request: the kernel reads positions and slots itself
-                items = None
-            else:
-                items = plans.get(rep)
-                if items is None:
-                    items = plans[rep] = seqlib.window_attn_items(plans["portions"], rep, dev)
+            items = plans.get(rep)
+            if items is None:
+                items = plans[rep] = seqlib.window_attn_items(plans["portions"], rep, dev)
+        if items is not None and self.fused_maps and seqlib.diff_attn_pair_ok(H, G, d, dv, self.dtype):
+            # prompt portions: both maps, the combine, the head norm and the gate in one kernel
+            seqlib.diff_attn_pair(q, H, G, d, dv, pool, cache.block_table, cache.page_size, items, window, m.keep_first, m.scale, mw.lam,
+                                  1.0 - m.diff, self.eps, gate, seqlib.GATE_SIGMOID, on)
+            return self._linear(on, mw.o, f32)
+        att = torch.empty(T, H * 2 * dv, device=dev, dtype=f32)
+        if tensor:       # items None: one row per request, the kernel reads positions and slots itself
             seqlib.window_attn_mma(q, H, G, d, dv, pool, cache.block_table, cache.page_size, items, pos, slot, window, m.scale, 0.0, None,
                                    att, maps=2, keep_first=m.keep_first)
         else:
             seqlib.window_attn(q, H, G, d, dv, pool, cache.block_table, cache.page_size, pos, slot, window, m.scale, 0.0, None, att,
                                maps=2, keep_first=m.keep_first)
-        on = torch.empty(T, H * dv, device=dev, dtype=self.dtype)
-        seqlib.diff_heads_gate(att, H, dv, mw.lam, 1.0 - m.diff, self.eps, z[:, mw.cols["g"]], seqlib.GATE_SIGMOID, on)
+        seqlib.diff_heads_gate(att, H, dv, mw.lam, 1.0 - m.diff, self.eps, gate, seqlib.GATE_SIGMOID, on)
         return self._linear(on, mw.o, f32)
 
     # ---- feed-forwards: update h32 (and write the next sublayer's normed input to xb_out) in place

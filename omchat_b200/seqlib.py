@@ -38,6 +38,8 @@ SIGNATURES = {
     "omc_window_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _F, _F, _P, _P, _I, _L, _P]),
     "omc_window_attn_mma_ok": (_I, [_I, _I, _I, _I]),
     "omc_window_attn_mma": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _I, _F, _F, _P, _P, _I, _L, _P]),
+    "omc_diff_attn_pair_ok": (_I, [_I, _I, _I, _I]),
+    "omc_diff_attn_pair": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _I, _I, _F, _F, _F, _F, _P, _L, _I, _P, _I, _L, _P]),
     "omc_embed_scale": (_I, [_P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _I, _L, _P]),
     "omc_rms_rows": (_I, [_P, _L, _P, _I, _I, _F, _P, _I, _L, _I, _I, _P]),
     "omc_norm_residual": (_I, [_P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
@@ -542,6 +544,27 @@ def window_attn_mma(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torc
                                     page_size, _ptr(items), items.shape[0] if items is not None else 0, _ptr(pos), _ptr(slot), window,
                                     keep_first, scale, softcap, _ptr(dist_bias), _ptr(out), _dt(out), out.stride(0), _stream())
     _check(rc, "omc_window_attn_mma")
+    return out
+
+
+def diff_attn_pair_ok(H: int, G: int, d: int, dv: int, dtype: torch.dtype) -> bool:
+    """Shapes the one-kernel differential attention of prompt portions takes (the tensor-core shapes whose two maps fit shared memory)."""
+    return dtype == torch.bfloat16 and bool(load().omc_diff_attn_pair_ok(H, G, d, dv))
+
+
+def diff_attn_pair(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                   items: torch.Tensor, window: int, keep_first: int, scale: float, lam: float, mult: float, eps: float,
+                   gate: Optional[torch.Tensor], gate_act: int, out: torch.Tensor):
+    """window_attn_mma(maps=2) + diff_heads_gate in one launch: q [T, H * 2 * d], gate fp32 [T, H * dv] -> out [T, H * dv]."""
+    _need_cuda(q, pool, block_table, items, gate, out)
+    assert q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert pool.is_contiguous() and pool.shape[-1] == G * (2 * d + dv) and block_table.is_contiguous()
+    assert items.dtype == torch.int32 and items.is_contiguous() and items.shape[1] == 4
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
+    rc = load().omc_diff_attn_pair(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, _ptr(pool), _ptr(block_table), block_table.shape[1],
+                                   page_size, _ptr(items), items.shape[0], window, keep_first, scale, lam, mult, eps, _ptr(gate),
+                                   gate.stride(0) if gate is not None else 0, gate_act, _ptr(out), _dt(out), out.stride(0), _stream())
+    _check(rc, "omc_diff_attn_pair")
     return out
 
 

@@ -314,6 +314,16 @@ def test_two_map_attention_with_window_and_kept_keys(H, G, d, dv, page, dtype, w
             out2 = torch.empty(n, H * 2 * dv, device=DEV)
             seqlib.window_attn_mma(qd, H, G, d, dv, pg.pool, pg.table, page, items, pos, slot, win, scale, 0.0, None, out2, maps=2, keep_first=keep)
             assert torch.allclose(out2.double().cpu().view(n, H, 2, dv), want, atol=tol, rtol=tol), (name, "tensor cores")
+            if items is not None and seqlib.diff_attn_pair_ok(H, G, d, dv, dtype):     # both maps and the combine in one kernel
+                lam, mult, eps = 0.45, 0.7, 1e-5
+                gate = torch.randn(n, H * dv + 2, generator=g, dtype=F64)
+                want_o = (O.unit_rms(want[:, :, 0] - lam * want[:, :, 1], eps) * mult).reshape(n, H * dv) * torch.sigmoid(gate[:, :H * dv])
+                out3 = torch.empty(n, H * dv, device=DEV)
+                seqlib.diff_attn_pair(qd, H, G, d, dv, pg.pool, pg.table, page, items, win, keep, scale, lam, mult, eps, _dev(gate)[:, :H * dv],
+                                      seqlib.GATE_SIGMOID, out3)
+                # the head norm divides by the size of a DIFFERENCE of two bf16-rounded maps: compare relative to the head's scale
+                err = (out3.double().cpu() - want_o).view(n, H, dv).abs().amax(-1) / want_o.view(n, H, dv).abs().amax(-1).clamp_min(1e-3)
+                assert float(err.max()) < 0.1 and float(err.median()) < 2e-2, (name, "paired maps", float(err.max()), float(err.median()))
 
 
 @pytest.mark.parametrize("dtype,mma", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
@@ -356,13 +366,21 @@ def test_one_key_that_stands_out_at_every_edge(dtype, mma, window, keep, page):
             else:
                 seqlib.window_attn(qd, H, G, d, dv, pg.pool, pg.table, page, pos, slot, window, scale, 0.0, None, out, maps=2, keep_first=keep)
             o = out.view(n, H, 2, dv)
+            paired = None
+            if mma and items is not None and seqlib.diff_attn_pair_ok(H, G, d, dv, dtype):
+                # the one-kernel path with lambda = 0: the first map alone, divided by its RMS over the head (1 / sqrt(dv) for a unit vector)
+                paired = torch.empty(n, H * dv, device=DEV)
+                seqlib.diff_attn_pair(qd, H, G, d, dv, pg.pool, pg.table, page, items, window, keep, scale, 0.0, dv ** -0.5, 0.0, None, 0, paired)
+                paired = paired.view(n, H, dv)
             for p, r in zip(rows, sel):
                 seen = mark < keep or p - mark < window
                 share = o[r, :, :, 1]                             # weight of the mark's value in every head and map
                 if seen:
                     assert (share > 0.99).all(), (mark, p, mode, "the mark must dominate")
+                    assert paired is None or (paired[r, :, 1] > 0.99).all(), (mark, p, mode, "paired maps: the mark must dominate")
                 else:
                     assert (share == 0).all(), (mark, p, mode, "the mark must be invisible")
+                    assert paired is None or (paired[r, :, 1] == 0).all(), (mark, p, mode, "paired maps: the mark must be invisible")
 
 
 @pytest.mark.parametrize("H,dv,lam,mult", [(6, 20, 0.37, 0.6), (1, 16, -1.2, 1.0), (3, 130, 0.0, 0.1)])
@@ -535,8 +553,8 @@ def test_plain_and_tensor_core_attention_agree_in_the_model():
     model, sd = build(cd, torch.bfloat16, seed=4)
     toks = tokens_for(cd, 180, 5)
     want = O.forward(sd, cd, toks)
-    for tc in (True, False):
-        model.decoder.tensor_attention = tc
+    for tc, fused in ((True, True), (True, False), (False, False)):
+        model.decoder.tensor_attention, model.decoder.fused_maps = tc, fused
         got = StepScheduler(model, max_tokens=256, slots=1).run_step([("a", toks, list(range(len(toks))))], ["a"])
         assert close(got, want, torch.bfloat16), row_errors(got, want).max()
 

@@ -8,6 +8,7 @@ Per size: prefill of `--prefill` x 1024-token prompts as ONE packed step through
 batch B and context ctx through the same scheduler (ms/step, tokens/s) - for the dense variant (every feed-forward dense: the equal-size
 comparison) and the mixed variant (every other feed-forward a mixture of experts) - and the new kernels timed alone on one layer's
 shapes against their rooflines, each beside the like kernel of the Tifisun path:
+  omc_diff_attn_pair                          prefill: both maps, combine, head norm and gate in one kernel; FLOPs as the next line
   omc_window_attn_mma, two maps + kept keys   prefill: FLOPs = rows x visible keys x heads x maps x 2 (dim + vdim) against the measured
                                               bf16 peak; decode: bytes of the visible keys and values against the copy bandwidth.
                                               Like kernel: the same entry with one map and no kept keys at equal head widths.
@@ -89,6 +90,11 @@ def kernels(z, n_seq, L, B, ctx):
     vis = n_seq * sum(min(p + 1, W) + max(0, min(keep, p + 1 - W)) for p in range(L))
     ms = timed(lambda: seqlib.window_attn_mma(qb, H, G, d, dv, pool, table, page, items, pos, slot, W, d ** -0.5, 0.0, None, att2, maps=2, keep_first=keep))
     out["diff_window_attn_prefill"] = rate(ms, flops=vis * H * 2 * 2.0 * (d + dv), ctas=int(items.shape[0]) * G * 2)
+    gate_a = torch.randn(T, H * dv, device=dev)
+    on_a = torch.empty(T, H * dv, device=dev, dtype=bf)
+    ms = timed(lambda: seqlib.diff_attn_pair(qb, H, G, d, dv, pool, table, page, items, W, keep, d ** -0.5, 0.4, 0.7, 1e-5, gate_a, seqlib.GATE_SIGMOID, on_a))
+    out["diff_attn_pair_prefill"] = rate(ms, flops=vis * H * 2 * 2.0 * (d + dv), ctas=int(items.shape[0]) * G)
+    del gate_a, on_a
     vis1 = n_seq * sum(min(p + 1, W) for p in range(L))
     ms = timed(lambda: seqlib.window_attn_mma(qb, H, G, 2 * d, dv, pool, table, page, items, pos, slot, W, d ** -0.5, 0.0, None, att1))
     out["tifisun_window_attn_prefill"] = rate(ms, flops=vis1 * H * 2.0 * (2 * d + dv), ctas=int(items.shape[0]) * G)
