@@ -249,7 +249,7 @@ def test_convolution_norm_and_append_in_one_launch(H, G, d, dv, taps, page, dtyp
     assert torch.allclose(rows[:, :nk], want_k, atol=tol, rtol=tol) and torch.allclose(rows[:, nk:], y[:, nq + nk:], atol=tol, rtol=tol)
 
 
-@pytest.mark.parametrize("M,N,K,batch", [(1, 13, 192, 1), (37, 24, 2048, 1), (9, 64, 256, 3), (300, 1, 45, 1)])
+@pytest.mark.parametrize("M,N,K,batch", [(1, 11, 200, 1), (37, 24, 2048, 1), (9, 64, 256, 3), (300, 1, 45, 1)])
 def test_linear_layer_with_few_outputs(M, N, K, batch):
     """Routers and gates: a handful of outputs over a long K, rows of strided buffers, a batch of column slices."""
     g = torch.Generator().manual_seed(M + N)
@@ -396,7 +396,7 @@ def test_differential_combine_head_norm_and_gate(H, dv, lam, mult):
         assert torch.allclose(out.double().cpu(), want, atol=tol, rtol=tol)
 
 
-@pytest.mark.parametrize("E,top", [(12, 2), (5, 5), (1, 1), (40, 7)])
+@pytest.mark.parametrize("E,top", [(10, 3), (5, 5), (1, 1), (40, 7)])
 def test_router_with_bias_and_softmax_over_the_chosen(E, top):
     g = torch.Generator().manual_seed(E)
     T = 21
