@@ -553,3 +553,166 @@ class FofisunConfig:
         return {"architecture": "Fofisun", "vocab": self.vocab_size, "width": self.hidden_size, "norm": {"eps": self.norm_eps},
                 "layers": out, "loop": {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times},
                 "kv_page_size": self.kv_page_size, "eos_token_id": self.eos_token_id, "pad_token_id": self.pad_token_id}
+
+
+# --------------------------------------------------------------------------------------------------------------------- Vefunex
+@dataclass
+class SoftmaxAttentionSpec:
+    """Causal softmax attention over all earlier keys with grouped heads. Which of the optional mechanisms a layer has:
+    rot (RotarySpec or None): pairwise-interleaved rotation of the first rot.dims dimensions of queries and keys; q_temp_coef /
+    q_temp_every: queries are multiplied by 1 + coef ln(floor((p + 1) / every) + 1) at position p (coef 0: off); value_norm: every
+    head's value is divided by its root mean square before it is cached; softcap: scores become softcap tanh(score / softcap)
+    (0: off); sink: one more learned term exp(sink_h) per head in the softmax denominator; gate: the concatenated heads are
+    multiplied by a sigmoid of a projection of the mixer's input."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: Optional[RotarySpec] = None
+    q_temp_coef: float = 0.0
+    q_temp_every: int = 1
+    value_norm: bool = False
+    softcap: float = 0.0
+    sink: bool = False
+    gate: bool = False
+
+
+@dataclass
+class SelectiveScanSpec:
+    """Selective state-space mixer: `inner` channels with `state` fp32 states each, a causal convolution of `conv` taps (with bias)
+    and silu in front, step sizes through a projection of rank dt_rank; S <- exp(dt A) S + dt x B, y = S C + D x, gated by silu(z)."""
+    inner: int
+    state: int
+    dt_rank: int
+    conv: int
+
+
+@dataclass
+class AttentionScanMixerSpec:
+    """Two mixers side by side on the same input: left_scale * attention + right_scale * selective scan."""
+    left: SoftmaxAttentionSpec
+    right: SelectiveScanSpec
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+
+
+@dataclass
+class GatedLinearAttentionSpec:
+    """Gated linear attention: per head S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T q_t with one decay per key channel,
+    alpha = sigmoid(low-rank projection + bias)^(1 / tau); queries scaled by dim^-1/2; the read-out is RMS-normed per head and gated
+    by silu of a projection."""
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+
+
+@dataclass
+class SigmoidMoeSpec:
+    """`experts` gated experts (silu, no biases) of width expert_ff; every token uses the `top` experts with the largest sigmoid
+    router scores; the scores are used as they are and multiply the experts' INPUT."""
+    experts: int
+    top: int
+    expert_ff: int
+
+
+@dataclass
+class VefunexLayerSpec:
+    type: str                      # 'attention' | 'parallel' | 'gla'
+    mixer: object                  # SoftmaxAttentionSpec | AttentionScanMixerSpec | GatedLinearAttentionSpec
+    mlp: Optional[SigmoidMoeSpec]
+
+
+@dataclass
+class VefunexConfig:
+    model_type: str = "vefunex"
+    vocab_size: int = 0
+    hidden_size: int = 0
+    norm_eps: float = 1e-6
+    residual_mult: float = 1.0
+    logit_softcap: float = 0.0     # logits become cap * tanh(logits / cap) (0: off)
+    canon_taps: int = 1            # taps of the convolution every sublayer's input passes (h + conv(h))
+    layers: List[VefunexLayerSpec] = field(default_factory=list)
+    kv_page_size: int = 64         # engine knob: tokens per cache page
+    eos_token_id: int = -1
+    pad_token_id: int = 0
+
+    MIXERS = ("attention", "parallel", "gla")
+
+    @staticmethod
+    def _attention(m: dict, i: int, *, value_norm: bool, sink: bool, gate: bool) -> SoftmaxAttentionSpec:
+        rot, qt = m.get("rot"), m.get("q_temp")
+        spec = SoftmaxAttentionSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                    scale=float(m["scale"]), rot=RotarySpec(dims=int(rot["dims"]), base=float(rot["base"])) if rot else None,
+                                    q_temp_coef=float(qt["coef"]) if qt else 0.0, q_temp_every=int(qt["every"]) if qt else 1,
+                                    value_norm=value_norm, softcap=float(m.get("softcap") or 0.0), sink=sink, gate=gate)
+        if spec.heads < 1 or spec.kv_heads < 1 or spec.heads % spec.kv_heads or spec.q_temp_every < 1 or \
+                (spec.rot is not None and (spec.rot.dims % 2 or not 0 <= spec.rot.dims <= spec.dim)):
+            raise ValueError(f"layer {i}: inconsistent attention sizes")
+        return spec
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "VefunexConfig":
+        layers = []
+        for i, ld in enumerate(d["layers"]):
+            typ, m = ld["type"], ld["mixer"]
+            if typ == "attention":
+                mix = cls._attention(m, i, value_norm=True, sink=False, gate=False)
+            elif typ == "parallel":
+                r = m["right"]
+                right = SelectiveScanSpec(inner=int(r["inner"]), state=int(r["state"]), dt_rank=int(r["dt_rank"]), conv=int(r["conv"]))
+                if min(right.inner, right.state, right.dt_rank, right.conv) < 1:
+                    raise ValueError(f"layer {i}: inconsistent selective-scan sizes")
+                mix = AttentionScanMixerSpec(left=cls._attention(m["left"], i, value_norm=False, sink=True, gate=True), right=right,
+                                             left_scale=float(m.get("left_scale", 1.0)), right_scale=float(m.get("right_scale", 1.0)))
+            elif typ == "gla":
+                mix = GatedLinearAttentionSpec(heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), tau=float(m["tau"]))
+                if min(mix.heads, mix.dim, mix.vdim) < 1 or not mix.tau > 0:
+                    raise ValueError(f"layer {i}: inconsistent gated-linear-attention sizes")
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {typ!r}")
+            md, mlp = ld.get("mlp"), None
+            if md:
+                if md.get("kind", "moe") != "moe":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {md.get('kind')!r}")
+                mlp = SigmoidMoeSpec(experts=int(md["router"]["experts"]), top=int(md["router"]["top"]), expert_ff=int(md["expert"]["ff"]))
+                if not 1 <= mlp.top <= mlp.experts or mlp.expert_ff < 1:
+                    raise ValueError(f"layer {i}: top must be between 1 and the number of experts")
+            layers.append(VefunexLayerSpec(type=typ, mixer=mix, mlp=mlp))
+        taps = int((d.get("canon") or {}).get("taps", 1))
+        if taps < 1:
+            raise ValueError("canon.taps must be at least 1")
+        return cls(vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)),
+                   residual_mult=float(d.get("residual_mult", 1.0)), logit_softcap=float(d.get("logit_softcap") or 0.0), canon_taps=taps,
+                   layers=layers, kv_page_size=int(d.get("kv_page_size", 64)), eos_token_id=int(d.get("eos_token_id", -1)),
+                   pad_token_id=int(d.get("pad_token_id", 0)))
+
+    def to_dict(self) -> dict:
+        """The config.json form (round-trips through from_dict)."""
+        def att(a: SoftmaxAttentionSpec) -> dict:
+            md = {"dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "scale": a.scale, "vdim": a.vdim}
+            if a.rot is not None:
+                md["rot"] = {"base": a.rot.base, "dims": a.rot.dims}
+            if a.q_temp_coef:
+                md["q_temp"] = {"coef": a.q_temp_coef, "every": a.q_temp_every}
+            if a.softcap:
+                md["softcap"] = a.softcap
+            return md
+        out = []
+        for l in self.layers:
+            m = l.mixer
+            if l.type == "attention":
+                md = att(m)
+            elif l.type == "parallel":
+                md = {"left": att(m.left), "left_scale": m.left_scale, "right_scale": m.right_scale,
+                      "right": {"conv": m.right.conv, "dt_rank": m.right.dt_rank, "inner": m.right.inner, "state": m.right.state}}
+            else:
+                md = {"dim": m.dim, "heads": m.heads, "tau": m.tau, "vdim": m.vdim}
+            mlp = None
+            if l.mlp is not None:
+                mlp = {"expert": {"ff": l.mlp.expert_ff}, "kind": "moe", "router": {"experts": l.mlp.experts, "top": l.mlp.top}}
+            out.append({"type": l.type, "mixer": md, "mlp": mlp})
+        return {"architecture": "Vefunex", "vocab": self.vocab_size, "width": self.hidden_size, "norm": {"eps": self.norm_eps},
+                "residual_mult": self.residual_mult, "logit_softcap": self.logit_softcap, "canon": {"taps": self.canon_taps}, "layers": out,
+                "kv_page_size": self.kv_page_size, "eos_token_id": self.eos_token_id, "pad_token_id": self.pad_token_id}

@@ -20,7 +20,7 @@ constexpr int kRouteWarps = 4;
 // One warp per row. Shared memory per warp: s[E_tot] (softmax scores) and ch[E_tot] (choice values, -inf once taken).
 __global__ void __launch_bounds__(kRouteWarps * 32) router_topk_kernel(const float* __restrict__ z, long long ldz, int T, int E_tot,
                                                                        int experts, int top, const float* __restrict__ correction,
-                                                                       const float* __restrict__ bias, int renorm,
+                                                                       const float* __restrict__ bias, int renorm, int score,
                                                                        int has_gate, int32_t* __restrict__ ids, float* __restrict__ w,
                                                                        float* __restrict__ gate, int32_t* __restrict__ counts) {
   extern __shared__ float sm[];
@@ -37,18 +37,26 @@ __global__ void __launch_bounds__(kRouteWarps * 32) router_topk_kernel(const flo
     mx = fmaxf(mx, v);
   }
   mx = seq_warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E_tot; e += 32) {
-    const float p = expf(ch[e] - mx);
-    s[e] = p;
-    sum += p;
-  }
-  sum = seq_warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int e = lane; e < E_tot; e += 32) {
-    const float p = s[e] * inv;
-    s[e] = p;
-    if (correction != nullptr) ch[e] = p + correction[e];   // without a correction the choice is made on the logits themselves
+  if (score == OMC_ROUTER_SIGMOID) {   // every output scored on its own; the sigmoid is monotonic, so the logits choose
+    for (int e = lane; e < E_tot; e += 32) {
+      const float p = 1.f / (1.f + expf(-ch[e]));
+      s[e] = p;
+      if (correction != nullptr) ch[e] = p + correction[e];
+    }
+  } else {
+    float sum = 0.f;
+    for (int e = lane; e < E_tot; e += 32) {
+      const float p = expf(ch[e] - mx);
+      s[e] = p;
+      sum += p;
+    }
+    sum = seq_warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < E_tot; e += 32) {
+      const float p = s[e] * inv;
+      s[e] = p;
+      if (correction != nullptr) ch[e] = p + correction[e];   // without a correction the choice is made on the logits themselves
+    }
   }
   __syncwarp();
   for (int k = 0; k < top; ++k) {
@@ -114,7 +122,8 @@ template <typename TT>
 __global__ void __launch_bounds__(128) moe_scatter_rows_kernel(const TT* __restrict__ x, long long ldx, int C,
                                                                const int32_t* __restrict__ ids, int top, int experts,
                                                                const int32_t* __restrict__ seg_start, int32_t* __restrict__ cursor,
-                                                               int32_t* __restrict__ slot_of, TT* __restrict__ xs, long long ldxs) {
+                                                               int32_t* __restrict__ slot_of, TT* __restrict__ xs, long long ldxs,
+                                                               const float* __restrict__ row_w) {
   __shared__ int s_slot[32];
   const int t = blockIdx.x;
   if (threadIdx.x < top) {
@@ -128,7 +137,12 @@ __global__ void __launch_bounds__(128) moe_scatter_rows_kernel(const TT* __restr
   for (int k = 0; k < top; ++k) {
     const int sl = s_slot[k];
     if (sl < 0) continue;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) xs[(long long)sl * ldxs + c] = x[(long long)t * ldx + c];
+    if (row_w != nullptr) {   // the mixing weight multiplies the expert's INPUT
+      const float wk = row_w[(long long)t * top + k];
+      for (int c = threadIdx.x; c < C; c += blockDim.x) stf(xs + (long long)sl * ldxs + c, wk * ldf(x + (long long)t * ldx + c));
+    } else {
+      for (int c = threadIdx.x; c < C; c += blockDim.x) xs[(long long)sl * ldxs + c] = x[(long long)t * ldx + c];
+    }
   }
 }
 
@@ -139,7 +153,8 @@ __global__ void __launch_bounds__(256) moe_plan_scatter_small_kernel(int32_t* __
                                                                      int32_t* __restrict__ seg_start, int32_t* __restrict__ tile_group,
                                                                      const TT* __restrict__ x, long long ldx, int T, int C,
                                                                      const int32_t* __restrict__ ids, int top,
-                                                                     int32_t* __restrict__ slot_of, TT* __restrict__ xs, long long ldxs) {
+                                                                     int32_t* __restrict__ slot_of, TT* __restrict__ xs, long long ldxs,
+                                                                     const float* __restrict__ row_w) {
   extern __shared__ int32_t s_seg[];  // [experts]: next free row of every expert's segment
   __shared__ int s_slot[32];
   for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) tile_group[i] = -1;
@@ -170,7 +185,12 @@ __global__ void __launch_bounds__(256) moe_plan_scatter_small_kernel(int32_t* __
     for (int k = 0; k < top; ++k) {
       const int sl = s_slot[k];
       if (sl < 0) continue;
-      for (int c = threadIdx.x; c < C; c += blockDim.x) xs[(long long)sl * ldxs + c] = x[(long long)t * ldx + c];
+      const float wk = row_w != nullptr ? row_w[(long long)t * top + k] : 1.f;
+      if (row_w != nullptr) {
+        for (int c = threadIdx.x; c < C; c += blockDim.x) stf(xs + (long long)sl * ldxs + c, wk * ldf(x + (long long)t * ldx + c));
+      } else {
+        for (int c = threadIdx.x; c < C; c += blockDim.x) xs[(long long)sl * ldxs + c] = x[(long long)t * ldx + c];
+      }
     }
     __syncthreads();
   }
@@ -222,13 +242,60 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const float* __re
   for (int c = threadIdx.x; c < C; c += blockDim.x) stf(xb + (long long)t * ldxb + c, srow[c] * rn * (1.f + ldf(w_next + c)));
 }
 
+
+// Combine + residual + depth-weighted average of the layer outputs, one pass over the row:
+//   y = sum_j (w[t, j] or 1) * ys[slot_of[t, j]]            (ys NULL: no feed-forward, y = 0)
+//   xn = x[t] + a1 * y1[t] + a2 * y2[t] + mult * y           -> streams[n_streams - 1][t]   (this layer's result; y1 / y2: sublayer
+//                                                               outputs that have not entered the stream yet, NULL: none)
+//   out[t] = sum_{j < n_streams} coef[j] * streams[j][t]     (coef NULL: out = xn)
+// streams[j] = streams + j * stream_stride: the embedding output and every earlier layer's result.
+template <typename TW>
+__global__ void __launch_bounds__(256) moe_combine_depth_kernel(const float* __restrict__ ys, long long ldys, const int32_t* __restrict__ slot_of,
+                                                                const float* __restrict__ w, int top, const float* __restrict__ x,
+                                                                long long ldx, const float* __restrict__ y1, long long ld1, float a1,
+                                                                const float* __restrict__ y2, long long ld2, float a2, float mult,
+                                                                float* __restrict__ streams,
+                                                                long long stream_stride, long long lds, int n_streams,
+                                                                const TW* __restrict__ coef, float* __restrict__ out, long long ldo, int C) {
+  __shared__ int s_slot[32];
+  __shared__ float s_w[32];
+  const long long t = blockIdx.x;
+  if (ys != nullptr && threadIdx.x < top) {
+    s_slot[threadIdx.x] = slot_of[t * top + threadIdx.x];
+    s_w[threadIdx.x] = w != nullptr ? w[t * top + threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float xn = x[t * ldx + c];
+    if (y1 != nullptr) xn = fmaf(a1, y1[t * ld1 + c], xn);
+    if (y2 != nullptr) xn = fmaf(a2, y2[t * ld2 + c], xn);
+    if (ys != nullptr) {
+      float y = 0.f;
+      for (int k = 0; k < top; ++k) {
+        const int sl = s_slot[k];
+        if (sl >= 0) y = fmaf(s_w[k], ys[(long long)sl * ldys + c], y);
+      }
+      xn = fmaf(mult, y, xn);
+    }
+    if (streams != nullptr) streams[(long long)(n_streams - 1) * stream_stride + t * lds + c] = xn;
+    float o = xn;
+    if (coef != nullptr) {
+      o = 0.f;
+      for (int j = 0; j + 1 < n_streams; ++j) o = fmaf(ldf(coef + j), streams[(long long)j * stream_stride + t * lds + c], o);
+      o = fmaf(ldf(coef + n_streams - 1), xn, o);
+    }
+    out[t * ldo + c] = o;
+  }
+}
+
 }  // namespace omc
 
 using namespace omc;
 
 extern "C" int omc_router_topk(const float* z, long long ldz, int T, int E_tot, int experts, int top, const float* correction,
-                               const float* bias, int renorm, int has_gate, int32_t* ids, float* w, float* gate, int32_t* counts,
+                               const float* bias, int renorm, int score, int has_gate, int32_t* ids, float* w, float* gate, int32_t* counts,
                                void* stream) {
+  if (score != OMC_ROUTER_SOFTMAX && score != OMC_ROUTER_SIGMOID) return set_error(OMC_ERR_ARG, "omc_router_topk: unknown score function");
   if (z == nullptr || ids == nullptr || w == nullptr || counts == nullptr || T < 0 || E_tot <= 0 || experts < 0 || experts > E_tot ||
       top <= 0 || top > E_tot || (has_gate && gate == nullptr))
     return set_error(OMC_ERR_ARG, "omc_router_topk: bad argument");
@@ -240,7 +307,7 @@ extern "C" int omc_router_topk(const float* z, long long ldz, int T, int E_tot, 
     if (e != cudaSuccess) return set_error(OMC_ERR_CUDA, cudaGetErrorString(e));
   }
   router_topk_kernel<<<(T + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
-      z, ldz, T, E_tot, experts, top, correction, bias, renorm, has_gate, ids, w, gate, counts);
+      z, ldz, T, E_tot, experts, top, correction, bias, renorm, score, has_gate, ids, w, gate, counts);
   return check_launch("omc_router_topk");
 }
 
@@ -253,7 +320,8 @@ extern "C" int omc_moe_plan_tiles(int32_t* counts, int experts, int tile, int ma
 }
 
 extern "C" int omc_moe_scatter_rows(const void* x, int dt, long long ldx, int T, int C, const int32_t* ids, int top, int experts,
-                                    const int32_t* seg_start, int32_t* cursor, int32_t* slot_of, void* xs, long long ldxs, void* stream) {
+                                    const int32_t* seg_start, int32_t* cursor, int32_t* slot_of, void* xs, long long ldxs, const float* row_w,
+                                    void* stream) {
   if (x == nullptr || ids == nullptr || seg_start == nullptr || cursor == nullptr || slot_of == nullptr || xs == nullptr || T < 0 ||
       C <= 0 || top <= 0 || top > 32)
     return set_error(OMC_ERR_ARG, "omc_moe_scatter_rows: bad argument");
@@ -261,14 +329,14 @@ extern "C" int omc_moe_scatter_rows(const void* x, int dt, long long ldx, int T,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   OMC_DT_SWITCH(dt, TT, {
     moe_scatter_rows_kernel<TT><<<T, 128, 0, st>>>(static_cast<const TT*>(x), ldx, C, ids, top, experts, seg_start, cursor, slot_of,
-                                                   static_cast<TT*>(xs), ldxs);
+                                                   static_cast<TT*>(xs), ldxs, row_w);
   })
   return check_launch("omc_moe_scatter_rows");
 }
 
 extern "C" int omc_moe_plan_scatter_small(int32_t* counts, int experts, int tile, int max_tiles, int32_t* seg_start, int32_t* tile_group,
                                           const void* x, int dt, long long ldx, int T, int C, const int32_t* ids, int top, int32_t* slot_of,
-                                          void* xs, long long ldxs, void* stream) {
+                                          void* xs, long long ldxs, const float* row_w, void* stream) {
   if (counts == nullptr || seg_start == nullptr || tile_group == nullptr || x == nullptr || ids == nullptr || slot_of == nullptr ||
       xs == nullptr || experts <= 0 || experts > 8192 || tile <= 0 || max_tiles <= 0 || T < 0 || C <= 0 || top <= 0 || top > 32)
     return set_error(OMC_ERR_ARG, "omc_moe_plan_scatter_small: bad argument");
@@ -276,7 +344,7 @@ extern "C" int omc_moe_plan_scatter_small(int32_t* counts, int experts, int tile
   OMC_DT_SWITCH(dt, TT, {
     moe_plan_scatter_small_kernel<TT><<<1, 256, experts * sizeof(int32_t), st>>>(counts, experts, tile, max_tiles, seg_start, tile_group,
                                                                                 static_cast<const TT*>(x), ldx, T, C, ids, top, slot_of,
-                                                                                static_cast<TT*>(xs), ldxs);
+                                                                                static_cast<TT*>(xs), ldxs, row_w);
   })
   return check_launch("omc_moe_plan_scatter_small");
 }
@@ -299,4 +367,20 @@ extern "C" int omc_moe_combine_norm(const float* ys, long long ldys, const int32
                                                           h32, ldh, static_cast<const TW*>(w_next), static_cast<TB*>(xb), ldxb, C);
   }))
   return check_launch("omc_moe_combine_norm");
+}
+
+extern "C" int omc_moe_combine_depth(const float* ys, long long ldys, const int32_t* slot_of, const float* w, int top, const float* x,
+                                     long long ldx, const float* y1, long long ld1, float a1, const float* y2, long long ld2, float a2,
+                                     float mult, float* streams, long long stream_stride, long long lds, int n_streams,
+                                     const void* coef, int coef_dt, float* out, long long ldo, int T, int C, void* stream) {
+  if (x == nullptr || out == nullptr || T < 0 || C <= 0 || (ys != nullptr && (slot_of == nullptr || top <= 0 || top > 32)) ||
+      (coef != nullptr && (streams == nullptr || n_streams < 1)) || (streams != nullptr && n_streams < 1))
+    return set_error(OMC_ERR_ARG, "omc_moe_combine_depth: bad argument");
+  if (T == 0) return OMC_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OMC_DT_SWITCH(coef_dt, TW, {
+    moe_combine_depth_kernel<TW><<<T, 256, 0, st>>>(ys, ldys, slot_of, w, top, x, ldx, y1, ld1, a1, y2, ld2, a2, mult, streams, stream_stride, lds, n_streams,
+                                                    static_cast<const TW*>(coef), out, ldo, C);
+  })
+  return check_launch("omc_moe_combine_depth");
 }

@@ -165,6 +165,7 @@ __device__ __forceinline__ float glu_pair(float g, float u, const GluParams& p) 
   if (p.act == OMC_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
   if (p.act == OMC_ACT_GELU_ERF) return 0.5f * g * (1.f + erff(g * 0.70710678118654752f)) * u;
   if (p.act == OMC_ACT_RELU2) return fmaxf(g, 0.f) * fmaxf(g, 0.f) * u;
+  if (p.act == OMC_ACT_SILU) return g / (1.f + expf(-g)) * u;
   return g * u;
 }
 
@@ -186,6 +187,28 @@ __global__ void __launch_bounds__(256) glu_mul_kernel(const TZ* __restrict__ z, 
   } else {
     stf(y + t * ldy + c, glu_pair(ldf(z + t * ldz + c), ldf(z + t * ldz + n + c), gp));
   }
+}
+
+
+// y[t, c] = tanh(alpha * x[t, c]) * w[c] + b[c]: a norm without statistics (alpha one scalar in device memory).
+template <typename TW, typename TY>
+__global__ void __launch_bounds__(256) dyt_rows_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ alpha_p,
+                                                       const TW* __restrict__ w, const TW* __restrict__ b, TY* __restrict__ y, long long ldy,
+                                                       int C, long long total) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const long long t = e / C;
+  const int c = (int)(e - t * C);
+  stf(y + t * ldy + c, fmaf(tanhf(*alpha_p * x[t * ldx + c]), ldf(w + c), ldf(b + c)));
+}
+
+// x[t, c] <- cap * tanh(x[t, c] / cap), in place.
+__global__ void __launch_bounds__(256) tanh_cap_rows_kernel(float* __restrict__ x, long long ldx, int cols, long long total, float cap) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const long long t = e / cols;
+  float* p = x + t * ldx + (e - t * cols);
+  *p = cap * tanhf(*p / cap);
 }
 
 }  // namespace omc
@@ -269,4 +292,26 @@ extern "C" int omc_embed_sinusoid(const int32_t* ids, const int32_t* pos, int T,
     embed_sinusoid_kernel<TT><<<T, 256, 0, st>>>(ids, pos, static_cast<const TT*>(table), C, vocab, scale, freq, h32, ldh);
   })
   return check_launch("omc_embed_sinusoid");
+}
+
+extern "C" int omc_dyt_rows(const float* x, long long ldx, const float* alpha, const void* w, const void* b, int w_dt, void* y, int y_dt,
+                            long long ldy, int rows, int C, void* stream) {
+  if (x == nullptr || alpha == nullptr || w == nullptr || b == nullptr || y == nullptr || rows < 0 || C <= 0)
+    return set_error(OMC_ERR_ARG, "omc_dyt_rows: bad argument");
+  if (rows == 0) return OMC_OK;
+  const long long total = (long long)rows * C;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OMC_DT_SWITCH(w_dt, TW, OMC_DT_SWITCH(y_dt, TY, {
+    dyt_rows_kernel<TW, TY><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(x, ldx, alpha, static_cast<const TW*>(w), static_cast<const TW*>(b),
+                                                                            static_cast<TY*>(y), ldy, C, total);
+  }))
+  return check_launch("omc_dyt_rows");
+}
+
+extern "C" int omc_tanh_cap_rows(float* x, long long ldx, int rows, int cols, float cap, void* stream) {
+  if (x == nullptr || rows < 0 || cols <= 0 || !(cap > 0.f)) return set_error(OMC_ERR_ARG, "omc_tanh_cap_rows: bad argument");
+  if (rows == 0) return OMC_OK;
+  const long long total = (long long)rows * cols;
+  tanh_cap_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, ldx, cols, total, cap);
+  return check_launch("omc_tanh_cap_rows");
 }

@@ -21,6 +21,9 @@ namespace omc {
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+// sigmoid(z)^p - 1 = expm1(p * log sigmoid(z)), log sigmoid(z) = -softplus(-z). The decay is kept as its distance from 1: rounded to
+// fp32 itself, a decay close to 1 loses most of the digits of 1 - decay, and the state multiplies by it once per token.
+__device__ __forceinline__ float sigmoid_pow_m1_f(float z, float p) { return expm1f(-p * softplus_f(-z)); }
 
 // ---- causal convolution (+ silu) (+ unit vectors) ---------------------------------------------------------------------------
 // One CTA per (1 or 8 consecutive rows, block of channels; blocks are whole unit-vector groups). Tap j of `taps` multiplies the input
@@ -30,11 +33,11 @@ __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + lo
 constexpr int kConvRows = 8;    // rows per CTA of a long step: neighbouring rows read each other's inputs, which then come from L1
 constexpr int kConvMaxTaps = 32;
 
-template <typename TW>
+template <typename TW, typename TY>
 __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __restrict__ x, long long ldx, int T, int ch, int ch_block,
-                                                               int rows_per_cta, const TW* __restrict__ w, int taps,
+                                                               int rows_per_cta, const TW* __restrict__ w, const TW* __restrict__ bias, int taps,
                                                                const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
-                                                               float* __restrict__ state, float* __restrict__ y, long long ldy,
+                                                               float* __restrict__ state, TY* __restrict__ y, long long ldy,
                                                                int unit_channels, int unit_group, float unit_eps, int scaled_channels,
                                                                float unit_mult, int save_here, int act) {
   extern __shared__ float tile[];  // [rows_per_cta][ch_block]
@@ -52,8 +55,9 @@ __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __re
   __syncthreads();
   for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) {
     const int c = c0 + cl;
+    const float b0 = bias != nullptr ? ldf(bias + c) : 0.f;
     for (int r = 0; r < nr; ++r) {
-      float acc = 0.f;
+      float acc = b0;
 #pragma unroll 4
       for (int j = 0; j < taps; ++j) {
         const float* q = src[r][j];
@@ -81,7 +85,7 @@ __global__ void __launch_bounds__(256) causal_conv_silu_kernel(const float* __re
   __syncthreads();
   for (int e = threadIdx.x; e < nr * nc; e += blockDim.x) {
     const int r = e / nc, cl = e - r * nc;
-    y[(long long)(t0 + r) * ldy + c0 + cl] = tile[r * ch_block + cl];
+    stf(y + (long long)(t0 + r) * ldy + c0 + cl, tile[r * ch_block + cl]);
   }
 }
 
@@ -175,7 +179,11 @@ struct ScanArgs {
   const float* v;      // [T, ldv]: head h at columns h * vdim
   long long ldq, ldk, ldv;
   int silu_in;         // q, k, v pass silu on the way in
-  int decay_mode;      // 0: decay_const[h]; 1: a[t, h]; 2: a[t, h * dim + i]  (1, 2: g = exp(-exp(A_log[h]) softplus(a + dt_bias))); 3: g = a[t, h * dim + i]
+  int decay_mode;      // 0: decay_const[h]; 1: a[t, h]; 2: a[t, h * dim + i]  (1, 2: g = exp(-exp(A_log[h]) softplus(a + dt_bias))); 3: g = a[t, h * dim + i];
+                       // 4: g = sigmoid(a[t, h * dim + i] + dt_bias[h * dim + i])^decay_pow; 5: a[t, h * dim + i] holds g - 1
+                       // (4 and 5 apply the decay as S + (g - 1) S)
+  float decay_pow;     // mode 4
+  float out_scale;     // o_t = out_scale * S^T q_t (a query scale, applied to the read-out)
   const float* decay_const;
   const float* a;
   long long lda;
@@ -230,7 +238,8 @@ __global__ void __launch_bounds__(kScanCols / 2 * kScanLanes) linear_state_scan_
   extern __shared__ __align__(16) float sm[];
   constexpr int PITCH = kScanLanes * (DPT + 4);
   const int dim = a.dim;
-  const bool chan = a.decay_mode >= 2;   // one decay per key channel: computed here (2) or given (3)
+  const bool chan = a.decay_mode >= 2;   // one decay per key channel: computed here (2, 4) or given (3, 5)
+  const bool minus1 = a.decay_mode >= 4;  // the staged value is the decay minus one
   const int stage_floats = kScanTok * PITCH * (chan ? 3 : 2) + kScanTok * kScanCols + 2 * kScanTok;
   const int h = blockIdx.y, kvh = h / (a.H / a.G);
   const int col0 = blockIdx.x * kScanCols;
@@ -307,7 +316,7 @@ __global__ void __launch_bounds__(kScanCols / 2 * kScanLanes) linear_state_scan_
     float* sv = sg + (chan ? kScanTok * PITCH : kScanTok);
     float* sb = sv + kScanTok * kScanCols;
     // raw inputs -> what the recurrence uses
-    if (a.silu_in || a.decay_mode == 2) {
+    if (a.silu_in || a.decay_mode == 2 || a.decay_mode == 4) {
       for (int e = tid; e < n * dim; e += blockDim.x) {
         const int tt = e / dim, i = e - tt * dim, at = tt * PITCH + scan_place<DPT>(i);
         if (a.silu_in) {
@@ -315,6 +324,7 @@ __global__ void __launch_bounds__(kScanCols / 2 * kScanLanes) linear_state_scan_
           sq[at] = silu_f(sq[at]);
         }
         if (a.decay_mode == 2) sg[at] = expf(-A * softplus_f(sg[at] + a.dt_bias[h * dim + i]));
+        else if (a.decay_mode == 4) sg[at] = sigmoid_pow_m1_f(sg[at] + (a.dt_bias != nullptr ? a.dt_bias[h * dim + i] : 0.f), a.decay_pow);
       }
     }
     if (a.silu_in)
@@ -338,8 +348,13 @@ __global__ void __launch_bounds__(kScanCols / 2 * kScanLanes) linear_state_scan_
         k2[r] = pack2(kv.x, kv.x), k2[r + 1] = pack2(kv.y, kv.y), k2[r + 2] = pack2(kv.z, kv.z), k2[r + 3] = pack2(kv.w, kv.w);
         if (chan) {
           const float4 gv = *reinterpret_cast<const float4*>(gr + r);
-          st[r] = mul2(st[r], pack2(gv.x, gv.x)), st[r + 1] = mul2(st[r + 1], pack2(gv.y, gv.y));
-          st[r + 2] = mul2(st[r + 2], pack2(gv.z, gv.z)), st[r + 3] = mul2(st[r + 3], pack2(gv.w, gv.w));
+          if (minus1) {
+            st[r] = fma2(st[r], pack2(gv.x, gv.x), st[r]), st[r + 1] = fma2(st[r + 1], pack2(gv.y, gv.y), st[r + 1]);
+            st[r + 2] = fma2(st[r + 2], pack2(gv.z, gv.z), st[r + 2]), st[r + 3] = fma2(st[r + 3], pack2(gv.w, gv.w), st[r + 3]);
+          } else {
+            st[r] = mul2(st[r], pack2(gv.x, gv.x)), st[r + 1] = mul2(st[r + 1], pack2(gv.y, gv.y));
+            st[r + 2] = mul2(st[r + 2], pack2(gv.z, gv.z)), st[r + 3] = mul2(st[r + 3], pack2(gv.w, gv.w));
+          }
         } else {
           st[r] = mul2(st[r], gh), st[r + 1] = mul2(st[r + 1], gh), st[r + 2] = mul2(st[r + 2], gh), st[r + 3] = mul2(st[r + 3], gh);
         }
@@ -383,8 +398,8 @@ __global__ void __launch_bounds__(kScanCols / 2 * kScanLanes) linear_state_scan_
       }
       if (lane == 0) {
         float* dst = a.out + (long long)(c0 + tt) * a.ldo + h * a.vdim + col;
-        if (ok0) dst[0] = o0;
-        if (ok1) dst[1] = o1;
+        if (ok0) dst[0] = o0 * a.out_scale;
+        if (ok1) dst[1] = o1 * a.out_scale;
       }
     }
     __syncthreads();   // the next iteration's copies overwrite the stage that was just read
@@ -400,17 +415,19 @@ __global__ void __launch_bounds__(kScanCols / 2 * kScanLanes) linear_state_scan_
 }
 
 // ---- elementwise preparation of a recurrence's inputs --------------------------------------------------------------------
-// In place over x[t, :cols]: op 1: silu; op 2: x <- exp(-exp(A_log[c / group]) * softplus(x + bias[c])), the per-channel decay.
+// In place over x[t, :cols]: op 1: silu; op 2: x <- exp(-exp(A_log[c / group]) * softplus(x + bias[c])), the per-channel decay;
+// op 3: x <- sigmoid(x + bias[c])^p - 1, the decay of a gated linear attention as its distance from 1.
 // The recurrence can do both itself while it stages its inputs; for long portions one pass here is cheaper than doing it in
 // every CTA that shares a head.
 __global__ void __launch_bounds__(256) map_rows_kernel(float* __restrict__ x, long long ldx, int cols, long long total, int op,
-                                                       const float* __restrict__ A_log, const float* __restrict__ bias, int group) {
+                                                       const float* __restrict__ A_log, const float* __restrict__ bias, int group, float p_exp) {
   const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= total) return;
   const long long t = e / cols;
   const int c = (int)(e - t * cols);
   float* p = x + t * ldx + c;
   if (op == 1) *p = silu_f(*p);
+  else if (op == 3) *p = sigmoid_pow_m1_f(*p + (bias != nullptr ? bias[c] : 0.f), p_exp);
   else *p = expf(-expf(A_log[c / group]) * softplus_f(*p + bias[c]));
 }
 
@@ -439,37 +456,220 @@ __global__ void __launch_bounds__(256) gated_rms_kernel(const float* __restrict_
   }
 }
 
+
+// ---- tanh norm + input convolution of a sublayer ----------------------------------------------------------------------------
+// What a sublayer of a "tanh-norm" decoder reads: with the stream row x (optionally first updated by the previous sublayer's
+// output, x <- x + a1 y1 + a2 y2), h = tanh(alpha x) * nw + nb (a norm without statistics) and u = h + sum_j cw[:, j] h_(t - taps + 1 + j),
+// a causal convolution over time per channel whose last taps - 1 inputs h live in a ring per slot like the other convolutions'.
+// A CTA owns (1 or 8 consecutive rows + the taps - 1 rows in front of them, a block of channels): h is evaluated once per tile
+// element into shared memory, then every row's taps read the tile, a ring entry or nothing.
+template <typename TW>
+__device__ __forceinline__ float dyt_f(float x, float alpha, const TW* __restrict__ nw, const TW* __restrict__ nb, int c) {
+  return fmaf(tanhf(alpha * x), ldf(nw + c), ldf(nb + c));
+}
+
+template <typename TW, typename TU>
+__global__ void __launch_bounds__(256) dyt_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ y1, long long ld1,
+                                                       float a1, const float* __restrict__ y2, long long ld2, float a2,
+                                                       float* __restrict__ x_out, long long ldxo, const float* __restrict__ alpha_p,
+                                                       const TW* __restrict__ nw, const TW* __restrict__ nb, const TW* __restrict__ cw, int taps,
+                                                       const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
+                                                       float* __restrict__ state, TU* __restrict__ u, long long ldu, int T, int C, int ch_block,
+                                                       int rows_per_cta, int save_here) {
+  extern __shared__ float tile[];  // [rows_per_cta + taps - 1][ch_block]: h of the halo rows, then of the CTA's own rows
+  __shared__ const float* src[kConvRows][kConvMaxTaps];   // where tap j of row r reads, as a pointer that takes the GLOBAL channel index
+  const int R = taps - 1;
+  const int t0 = blockIdx.x * rows_per_cta, nr = min(rows_per_cta, T - t0);
+  const int c0 = blockIdx.y * ch_block, nc = min(ch_block, C - c0);
+  const float alpha = *alpha_p;
+  if (threadIdx.x < nr * taps) {
+    const int r = threadIdx.x / taps, j = threadIdx.x - r * taps;
+    const int t = t0 + r, p = pos[t], s = slot[t], back = R - j, sp = p - back;
+    const float* q = nullptr;
+    if (sp >= 0) q = (back == 0 || (t - back >= 0 && slot[t - back] == s)) ? tile + (R + r - back) * ch_block - c0 : state + ((long long)s * R + sp % R) * C;
+    src[r][j] = q;
+  }
+  for (int e = threadIdx.x; e < (nr + R) * nc; e += blockDim.x) {
+    const int i = e / nc, cl = e - i * nc, c = c0 + cl, t = t0 - R + i;
+    float h = 0.f;
+    if (t >= 0) {
+      float xv = x[(long long)t * ldx + c];
+      if (y1 != nullptr) xv = fmaf(a1, y1[(long long)t * ld1 + c], xv);
+      if (y2 != nullptr) xv = fmaf(a2, y2[(long long)t * ld2 + c], xv);
+      if (i >= R && x_out != nullptr) x_out[(long long)t * ldxo + c] = xv;
+      h = dyt_f(xv, alpha, nw, nb, c);
+    }
+    tile[i * ch_block + cl] = h;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < nr * nc; e += blockDim.x) {
+    const int r = e / nc, cl = e - r * nc, c = c0 + cl;
+    const float h = tile[(R + r) * ch_block + cl];
+    float acc = h;
+    for (int j = 0; j < taps; ++j) {
+      const float* q = src[r][j];
+      if (q != nullptr) acc = fmaf(ldf(cw + (long long)c * taps + j), q[c], acc);
+    }
+    stf(u + (long long)(t0 + r) * ldu + c, acc);
+    // every row is a request of its own: nobody else reads this ring, and this thread's reads of channel c came first
+    if (save_here && R > 0) state[((long long)slot[t0 + r] * R + pos[t0 + r] % R) * C + c] = h;
+  }
+}
+
+// The ring update of a step whose requests may have several rows: h of the last taps - 1 rows of every request, recomputed from the
+// (already updated) stream rows.
+template <typename TW>
+__global__ void __launch_bounds__(256) dyt_state_save_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ alpha_p,
+                                                             const TW* __restrict__ nw, const TW* __restrict__ nb, int C, int R, int T,
+                                                             const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
+                                                             float* __restrict__ state) {
+  const int t = blockIdx.x;
+  const int s = slot[t];
+  if (t + R < T && slot[t + R] == s) return;
+  const float alpha = *alpha_p;
+  float* dst = state + ((long long)s * R + pos[t] % R) * C;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) dst[c] = dyt_f(x[(long long)t * ldx + c], alpha, nw, nb, c);
+}
+
+// ---- selective scan -------------------------------------------------------------------------------------------------------
+// Per channel c a state S[c, :N] (fp32, in the request's slot):  S <- exp(dt_c A[c, :]) * S + dt_c x_c B_t;  y_c = S . C_t + D_c x_c,
+// with dt = softplus(raw + bias) per channel and token, A = -exp(A_log), B_t / C_t shared by the channels; the output is gated,
+// y * silu(z). Channels are independent: a CTA owns a block of channels of one request's portion, LANES neighbouring lanes share a
+// channel (lane l holds the states l, l + LANES, ...), tokens go one after the other in chunks of kSelTok staged in shared memory.
+// A portion whose first row has position 0 starts from S = 0.
+constexpr int kSelTok = 16, kSelThreads = 128, kSelMaxPerLane = 8;
+
+struct SelArgs {
+  const void* x;
+  long long ldx;
+  const float* dt;
+  long long lddt;
+  const float* dt_bias;
+  const float* B;
+  long long ldb;
+  const float* Cm;
+  long long ldc;
+  const float* A_log;
+  const float* D;
+  const float* z;
+  long long ldz;
+  float* state;
+  void* y;
+  long long ldy;
+  const int32_t* row_begin;
+  const int32_t* pos;
+  const int32_t* slot;
+  int inner, N;
+};
+
+template <int LANES, typename TX, typename TY>
+__global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelArgs a) {
+  constexpr int CH = kSelThreads / LANES;
+  extern __shared__ float sm[];
+  float* s_dt = sm;                          // [tok][CH]
+  float* s_x = s_dt + kSelTok * CH;          // [tok][CH]
+  float* s_y = s_x + kSelTok * CH;           // [tok][CH]
+  float* s_B = s_y + kSelTok * CH;           // [tok][N]
+  float* s_C = s_B + kSelTok * a.N;          // [tok][N]
+  const int N = a.N, tid = threadIdx.x, lane = tid % LANES, cl = tid / LANES;
+  const int c0 = blockIdx.x * CH, c = c0 + cl, ncl = min(CH, a.inner - c0);
+  const bool live = c < a.inner;
+  const int r0 = a.row_begin[blockIdx.y], r1 = a.row_begin[blockIdx.y + 1];
+  if (r1 <= r0) return;
+  const bool fresh = a.pos[r0] == 0;
+  float* S = a.state + ((long long)a.slot[r0] * a.inner + (live ? c : 0)) * N;
+  float st[kSelMaxPerLane], A[kSelMaxPerLane];
+#pragma unroll
+  for (int r = 0; r < kSelMaxPerLane; ++r) {
+    const int n = lane + r * LANES;
+    const bool ok = live && n < N;
+    st[r] = (ok && !fresh) ? S[n] : 0.f;
+    A[r] = ok ? -expf(a.A_log[(long long)c * N + n]) : 0.f;
+  }
+  const float Dc = live ? a.D[c] : 0.f;
+  const TX* xg = static_cast<const TX*>(a.x);
+  TY* yg = static_cast<TY*>(a.y);
+  for (int t0 = r0; t0 < r1; t0 += kSelTok) {
+    const int n_tok = min(kSelTok, r1 - t0);
+    for (int e = tid; e < n_tok * ncl; e += kSelThreads) {
+      const int tt = e / ncl, j = e - tt * ncl;
+      s_dt[tt * CH + j] = softplus_f(a.dt[(long long)(t0 + tt) * a.lddt + c0 + j] + a.dt_bias[c0 + j]);
+      s_x[tt * CH + j] = ldf(xg + (long long)(t0 + tt) * a.ldx + c0 + j);
+    }
+    for (int e = tid; e < n_tok * N; e += kSelThreads) {
+      const int tt = e / N, n = e - tt * N;
+      s_B[e] = a.B[(long long)(t0 + tt) * a.ldb + n];
+      s_C[e] = a.Cm[(long long)(t0 + tt) * a.ldc + n];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < n_tok; ++tt) {
+      const float dt = s_dt[tt * CH + cl], xv = s_x[tt * CH + cl], dx = dt * xv;
+      const float* Bt = s_B + tt * N;
+      const float* Ct = s_C + tt * N;
+      float y = 0.f;
+#pragma unroll
+      for (int r = 0; r < kSelMaxPerLane; ++r) {
+        const int n = lane + r * LANES;
+        if (n < N) {
+          // the decay as S + (exp(dt A) - 1) S: a decay close to 1 would lose most of the digits of 1 - decay when rounded to
+          // fp32 itself, and that error grows with every token the state remembers
+          st[r] = fmaf(expm1f(dt * A[r]), st[r], st[r]) + dx * Bt[n];
+          y = fmaf(st[r], Ct[n], y);
+        }
+      }
+#pragma unroll
+      for (int m = 1; m < LANES; m <<= 1) y += __shfl_xor_sync(0xffffffffu, y, m);
+      if (lane == 0) s_y[tt * CH + cl] = fmaf(Dc, xv, y);
+    }
+    __syncthreads();
+    for (int e = tid; e < n_tok * ncl; e += kSelThreads) {
+      const int tt = e / ncl, j = e - tt * ncl;
+      float y = s_y[tt * CH + j];
+      if (a.z != nullptr) y *= silu_f(a.z[(long long)(t0 + tt) * a.ldz + c0 + j]);
+      stf(yg + (long long)(t0 + tt) * a.ldy + c0 + j, y);
+    }
+    // the next chunk's staging writes s_dt / s_x / s_B / s_C, which nobody reads any more; s_y is rewritten only after the next barrier
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < kSelMaxPerLane; ++r) {
+      const int n = lane + r * LANES;
+      if (n < N) S[n] = st[r];
+    }
+  }
+}
+
 }  // namespace omc
 
 using namespace omc;
 
-extern "C" int omc_causal_conv(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps,
-                               const int32_t* pos, const int32_t* slot, float* state, float* y, long long ldy, int act,
+extern "C" int omc_causal_conv(const float* x, long long ldx, int T, int ch, const void* w, const void* bias, int w_dt, int taps,
+                               const int32_t* pos, const int32_t* slot, float* state, void* y, int y_dt, long long ldy, int act,
                                int unit_channels, int unit_group, float unit_eps, int scaled_channels, float unit_mult,
                                int single_rows, void* stream) {
   if (x == nullptr || w == nullptr || pos == nullptr || slot == nullptr || y == nullptr || T < 0 || ch <= 0 || taps < 1 || taps > kConvMaxTaps ||
       (taps > 1 && state == nullptr) || (act != OMC_CONV_LINEAR && act != OMC_CONV_SILU) || unit_channels < 0 || unit_channels > ch || (unit_channels > 0 && (unit_group <= 0 || unit_channels % unit_group)) ||
       (unit_channels > 0 && scaled_channels % unit_group))
-    return set_error(OMC_ERR_ARG, "omc_causal_conv_silu: bad argument");
+    return set_error(OMC_ERR_ARG, "omc_causal_conv: bad argument");
   if (T == 0) return OMC_OK;
   // channel blocks of about 512 channels, whole unit-vector groups each
   int ch_block = 512;
   if (unit_channels > 0) ch_block = unit_group >= 512 ? unit_group : (512 / unit_group) * unit_group;
   if (ch_block > ch) ch_block = ch;
-  if ((size_t)ch_block * kConvRows * sizeof(float) > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: unit-vector group too wide for shared memory");
+  if ((size_t)ch_block * kConvRows * sizeof(float) > 200 * 1024) return set_error(OMC_ERR_SHAPE, "omc_causal_conv: unit-vector group too wide for shared memory");
   const int blocks = (ch + ch_block - 1) / ch_block;
-  if (blocks > 65535) return set_error(OMC_ERR_SHAPE, "omc_causal_conv_silu: too many channel blocks");
+  if (blocks > 65535) return set_error(OMC_ERR_SHAPE, "omc_causal_conv: too many channel blocks");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int rows_per_cta = T >= 256 ? kConvRows : 1;   // short steps (decode) keep one CTA per row: there are few rows to share anything
   const size_t smem = (size_t)ch_block * rows_per_cta * sizeof(float);
-  OMC_DT_SWITCH(w_dt, TW, {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(causal_conv_silu_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    causal_conv_silu_kernel<TW><<<dim3((T + rows_per_cta - 1) / rows_per_cta, blocks), 256, smem, st>>>(x, ldx, T, ch, ch_block, rows_per_cta, static_cast<const TW*>(w), taps, pos, slot, state, y,
-                                                                    ldy, unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
-                                                                    single_rows ? 1 : 0, act == OMC_CONV_SILU ? 1 : 0);
-  })
+  OMC_DT_SWITCH(w_dt, TW, OMC_DT_SWITCH(y_dt, TY, {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(causal_conv_silu_kernel<TW, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    causal_conv_silu_kernel<TW, TY><<<dim3((T + rows_per_cta - 1) / rows_per_cta, blocks), 256, smem, st>>>(
+        x, ldx, T, ch, ch_block, rows_per_cta, static_cast<const TW*>(w), static_cast<const TW*>(bias), taps, pos, slot, state,
+        static_cast<TY*>(y), ldy, unit_channels, unit_group, unit_eps, scaled_channels, unit_mult, single_rows ? 1 : 0, act == OMC_CONV_SILU ? 1 : 0);
+  }))
   if (taps > 1 && !single_rows) conv_state_save_kernel<<<dim3(T, (ch + 1023) / 1024), 256, 0, st>>>(x, ldx, ch, taps - 1, T, pos, slot, state);
-  return check_launch("omc_causal_conv_silu");
+  return check_launch("omc_causal_conv");
 }
 
 extern "C" int omc_conv_qk_norm_kv_store(const float* x, long long ldx, int T, int ch, const void* w, int w_dt, int taps, const int32_t* pos,
@@ -504,24 +704,24 @@ extern "C" int omc_causal_conv_silu(const float* x, long long ldx, int T, int ch
                                     const int32_t* pos, const int32_t* slot, float* state, float* y, long long ldy,
                                     int unit_channels, int unit_group, float unit_eps, int scaled_channels, float unit_mult,
                                     int single_rows, void* stream) {
-  return omc_causal_conv(x, ldx, T, ch, w, w_dt, taps, pos, slot, state, y, ldy, OMC_CONV_SILU, unit_channels, unit_group, unit_eps,
-                         scaled_channels, unit_mult, single_rows, stream);
+  return omc_causal_conv(x, ldx, T, ch, w, nullptr, w_dt, taps, pos, slot, state, y, OMC_DT_F32, ldy, OMC_CONV_SILU, unit_channels, unit_group,
+                         unit_eps, scaled_channels, unit_mult, single_rows, stream);
 }
 
 extern "C" int omc_linear_state_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
                                      int silu_in, int decay_mode, const float* decay_const, const float* a, long long lda,
                                      const float* A_log, const float* dt_bias, const float* beta, long long ldb, float* state,
                                      float* out, long long ldo, const int32_t* row_begin, int portions, const int32_t* pos,
-                                     const int32_t* slot, int H, int G, int dim, int vdim, void* stream) {
+                                     const int32_t* slot, int H, int G, int dim, int vdim, float decay_pow, float out_scale, void* stream) {
   if (q == nullptr || k == nullptr || v == nullptr || state == nullptr || out == nullptr || row_begin == nullptr || pos == nullptr ||
-      slot == nullptr || portions < 0 || H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || decay_mode < 0 || decay_mode > 3 ||
+      slot == nullptr || portions < 0 || H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || decay_mode < 0 || decay_mode > 5 ||
       (decay_mode == 0 && decay_const == nullptr) || (decay_mode != 0 && a == nullptr) ||
       ((decay_mode == 1 || decay_mode == 2) && (A_log == nullptr || dt_bias == nullptr)))
     return set_error(OMC_ERR_ARG, "omc_linear_state_scan: bad argument");
   if (portions == 0) return OMC_OK;
   if (dim > 256) return set_error(OMC_ERR_SHAPE, "omc_linear_state_scan: key width above 256");
   if (portions > 65535 || H > 65535) return set_error(OMC_ERR_SHAPE, "omc_linear_state_scan: more than 65535 portions or heads");
-  ScanArgs s{q, k, v, ldq, ldk, ldv, silu_in, decay_mode, decay_const, a, lda, A_log, dt_bias, beta, ldb, state, out, ldo,
+  ScanArgs s{q, k, v, ldq, ldk, ldv, silu_in, decay_mode, decay_pow, out_scale, decay_const, a, lda, A_log, dt_bias, beta, ldb, state, out, ldo,
              row_begin, pos, slot, H, G, dim, vdim};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int dpt = dim <= 32 ? 4 : (dim <= 64 ? 8 : (dim <= 128 ? 16 : 32));   // key channels per thread: dim / 8 lanes, rounded up to a float4
@@ -570,11 +770,71 @@ extern "C" int omc_gated_rms_rows(const float* x, long long ldx, int rows, int g
 }
 
 extern "C" int omc_map_rows(float* x, long long ldx, int rows, int cols, int op, const float* A_log, const float* bias, int group,
-                            void* stream) {
-  if (x == nullptr || rows < 0 || cols <= 0 || (op != 1 && op != 2) || (op == 2 && (A_log == nullptr || bias == nullptr || group <= 0)))
+                            float p_exp, void* stream) {
+  if (x == nullptr || rows < 0 || cols <= 0 || op < 1 || op > 3 || (op == 2 && (A_log == nullptr || bias == nullptr || group <= 0)))
     return set_error(OMC_ERR_ARG, "omc_map_rows: bad argument");
   if (rows == 0) return OMC_OK;
   const long long total = (long long)rows * cols;
-  map_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, ldx, cols, total, op, A_log, bias, group);
+  map_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, ldx, cols, total, op, A_log, bias, group, p_exp);
   return check_launch("omc_map_rows");
+}
+
+extern "C" int omc_dyt_conv(const float* x, long long ldx, const float* y1, long long ld1, float a1, const float* y2, long long ld2, float a2,
+                            float* x_out, long long ldxo, const float* alpha, const void* nw, const void* nb, const void* cw, int w_dt,
+                            int taps, const int32_t* pos, const int32_t* slot, float* state, void* u, int u_dt, long long ldu, int T, int C,
+                            int single_rows, void* stream) {
+  if (x == nullptr || alpha == nullptr || nw == nullptr || nb == nullptr || cw == nullptr || pos == nullptr || slot == nullptr || u == nullptr ||
+      T < 0 || C <= 0 || taps < 1 || taps > kConvMaxTaps || (taps > 1 && state == nullptr) || ((y1 != nullptr || y2 != nullptr) && x_out == nullptr) ||
+      (x_out == x && (y1 != nullptr || y2 != nullptr)))
+    return set_error(OMC_ERR_ARG, "omc_dyt_conv: bad argument");
+  if (T == 0) return OMC_OK;
+  const int ch_block = C < 512 ? C : 512;
+  const int blocks = (C + ch_block - 1) / ch_block;
+  if (blocks > 65535) return set_error(OMC_ERR_SHAPE, "omc_dyt_conv: too many channel blocks");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rows_per_cta = T >= 256 ? kConvRows : 1;
+  const size_t smem = (size_t)ch_block * (rows_per_cta + taps - 1) * sizeof(float);
+  const float* xs = (y1 != nullptr || y2 != nullptr) ? x_out : x;   // where the save kernel finds the updated stream
+  const long long ldxs = (y1 != nullptr || y2 != nullptr) ? ldxo : ldx;
+  OMC_DT_SWITCH(w_dt, TW, OMC_DT_SWITCH(u_dt, TU, {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(dyt_conv_kernel<TW, TU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    dyt_conv_kernel<TW, TU><<<dim3((T + rows_per_cta - 1) / rows_per_cta, blocks), 256, smem, st>>>(
+        x, ldx, y1, ld1, a1, y2, ld2, a2, x_out, ldxo, alpha, static_cast<const TW*>(nw), static_cast<const TW*>(nb), static_cast<const TW*>(cw),
+        taps, pos, slot, state, static_cast<TU*>(u), ldu, T, C, ch_block, rows_per_cta, single_rows ? 1 : 0);
+    if (taps > 1 && !single_rows)
+      dyt_state_save_kernel<TW><<<dim3(T, (C + 1023) / 1024), 256, 0, st>>>(xs, ldxs, alpha, static_cast<const TW*>(nw), static_cast<const TW*>(nb), C,
+                                                                           taps - 1, T, pos, slot, state);
+  }))
+  return check_launch("omc_dyt_conv");
+}
+
+extern "C" int omc_selective_scan(const void* x, int x_dt, long long ldx, const float* dt, long long lddt, const float* dt_bias, const float* B,
+                                  long long ldb, const float* Cm, long long ldc, const float* A_log, const float* D, const float* z, long long ldz,
+                                  float* state, void* y, int y_dt, long long ldy, const int32_t* row_begin, int portions, const int32_t* pos,
+                                  const int32_t* slot, int inner, int N, void* stream) {
+  if (x == nullptr || dt == nullptr || dt_bias == nullptr || B == nullptr || Cm == nullptr || A_log == nullptr || D == nullptr || state == nullptr ||
+      y == nullptr || row_begin == nullptr || pos == nullptr || slot == nullptr || portions < 0 || inner <= 0 || N <= 0)
+    return set_error(OMC_ERR_ARG, "omc_selective_scan: bad argument");
+  if (portions == 0) return OMC_OK;
+  if (N > 32 * kSelMaxPerLane) return set_error(OMC_ERR_SHAPE, "omc_selective_scan: more than 256 states per channel");
+  if (portions > 65535) return set_error(OMC_ERR_SHAPE, "omc_selective_scan: more than 65535 portions");
+  SelArgs s{x, ldx, dt, lddt, dt_bias, B, ldb, Cm, ldc, A_log, D, z, ldz, state, y, ldy, row_begin, pos, slot, inner, N};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int lanes = 1;
+  while (lanes * kSelMaxPerLane < N) lanes <<= 1;
+  const int ch = kSelThreads / lanes;
+  const size_t smem = sizeof(float) * ((size_t)3 * kSelTok * ch + 2 * (size_t)kSelTok * N);
+  dim3 grid((inner + ch - 1) / ch, portions);
+#define OMC_SEL_LAUNCH(L)                                                                             \
+  OMC_DT_SWITCH(x_dt, TX, OMC_DT_SWITCH(y_dt, TY, {                                                   \
+    selective_scan_kernel<L, TX, TY><<<grid, kSelThreads, smem, st>>>(s);                             \
+  }))
+  if (lanes == 1) { OMC_SEL_LAUNCH(1) }
+  else if (lanes == 2) { OMC_SEL_LAUNCH(2) }
+  else if (lanes == 4) { OMC_SEL_LAUNCH(4) }
+  else if (lanes == 8) { OMC_SEL_LAUNCH(8) }
+  else if (lanes == 16) { OMC_SEL_LAUNCH(16) }
+  else { OMC_SEL_LAUNCH(32) }
+#undef OMC_SEL_LAUNCH
+  return check_launch("omc_selective_scan");
 }

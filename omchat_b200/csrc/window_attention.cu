@@ -63,6 +63,72 @@ __global__ void __launch_bounds__(256) qk_norm_kv_store_kernel(const float* __re
   for (int c = threadIdx.x; c < nv; c += blockDim.x) stf(dst + nk + c, v[t * ldv + c]);
 }
 
+// Rows of a step for an attention with positions in the queries and keys themselves. Per head: the first rot_dims dimensions of
+// queries and keys are rotated pairwise - (u, v) at (2i, 2i + 1) becomes (u cos a - v sin a, v cos a + u sin a), a = position * freq[i],
+// the angle formed in fp32 - (freq NULL: no rotation); queries are multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)
+// (temp_coef 0: off); values are divided by their root mean square over each head's dv values when v_unit is set. Queries go to
+// q_out, keys and values to the cache row of (slot, position). One CTA per row.
+template <typename TC>
+__global__ void __launch_bounds__(256) pos_qkv_store_kernel(const float* __restrict__ q, long long ldq, int H, const float* __restrict__ k,
+                                                            long long ldk, int G, int d, const float* __restrict__ v, long long ldv, int dv,
+                                                            const float* __restrict__ freq, int rot_dims, float temp_coef, int temp_every,
+                                                            int v_unit, float eps, const int32_t* __restrict__ pos,
+                                                            const int32_t* __restrict__ slot, const int32_t* __restrict__ block_table,
+                                                            int max_pages, int page_size, TC* __restrict__ pool, TC* __restrict__ q_out,
+                                                            long long ldqo) {
+  extern __shared__ float cs[];   // [rot_dims / 2][2]: cos, sin
+  const long long t = blockIdx.x;
+  const int p = pos[t];
+  const int page = block_table[(long long)slot[t] * max_pages + p / page_size];
+  const int nk = G * d, nv = G * dv, half = freq != nullptr ? rot_dims / 2 : 0;
+  TC* dst = pool + ((long long)page * page_size + p % page_size) * (nk + nv);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float a = (float)p * freq[i];
+    cs[2 * i] = cosf(a);
+    cs[2 * i + 1] = sinf(a);
+  }
+  __syncthreads();
+  float temp = 1.f;
+  if (temp_coef != 0.f) temp = 1.f + temp_coef * logf((float)((p + 1) / temp_every) + 1.f);
+  const float* qr = q + t * ldq;
+  const float* kr = k + t * ldk;
+  // queries then keys: (head, pair) for the rotated part, single elements for the rest
+  const int qpairs = H * half, kpairs = G * half;
+  for (int e = threadIdx.x; e < qpairs + kpairs; e += blockDim.x) {
+    const bool isq = e < qpairs;
+    const int ee = isq ? e : e - qpairs, hh = ee / half, i = ee - hh * half;
+    const float* src = (isq ? qr : kr) + hh * d + 2 * i;
+    const float c = cs[2 * i], sn = cs[2 * i + 1], a0 = src[0], a1 = src[1];
+    const float r0 = a0 * c - a1 * sn, r1 = a1 * c + a0 * sn;
+    if (isq) {
+      stf(q_out + t * ldqo + hh * d + 2 * i, r0 * temp);
+      stf(q_out + t * ldqo + hh * d + 2 * i + 1, r1 * temp);
+    } else {
+      stf(dst + hh * d + 2 * i, r0);
+      stf(dst + hh * d + 2 * i + 1, r1);
+    }
+  }
+  const int rest = d - 2 * half;
+  for (int e = threadIdx.x; e < (H + G) * rest; e += blockDim.x) {
+    const int hh = e / rest, c = 2 * half + (e - hh * rest);
+    if (hh < H) stf(q_out + t * ldqo + hh * d + c, qr[hh * d + c] * temp);
+    else stf(dst + (hh - H) * d + c, kr[(hh - H) * d + c]);
+  }
+  const float* vr = v + t * ldv;
+  if (!v_unit) {
+    for (int c = threadIdx.x; c < nv; c += blockDim.x) stf(dst + nk + c, vr[c]);
+  } else {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int g = warp; g < G; g += nw) {
+      float ss = 0.f;
+      for (int c = lane; c < dv; c += 32) ss = fmaf(vr[g * dv + c], vr[g * dv + c], ss);
+      ss = seq_warp_sum(ss);
+      const float rstd = 1.f / sqrtf(ss / (float)dv + eps);
+      for (int c = lane; c < dv; c += 32) stf(dst + nk + g * dv + c, vr[g * dv + c] * rstd);
+    }
+  }
+}
+
 template <typename TQ, typename TC, typename TY>
 __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(const TQ* __restrict__ q, long long ldq, int H, int G, int d,
                                                                      int dv, int maps, const TC* __restrict__ pool,
@@ -70,7 +136,8 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(const TQ* _
                                                                      int page_size, const int32_t* __restrict__ pos,
                                                                      const int32_t* __restrict__ slot, int window, int keep_first,
                                                                      float scale, float softcap, const float* __restrict__ dist_bias,
-                                                                     TY* __restrict__ out, long long ldo) {
+                                                                     const float* __restrict__ sink, const float* __restrict__ gate,
+                                                                     long long ldg, int gate_act, TY* __restrict__ out, long long ldo) {
   extern __shared__ float sm[];  // q [d] | acc [warps][dv] | m [warps] | l [warps]
   // blockIdx.y = head * maps + map: queries and outputs are laid out [head][map][.], keys [key/value head][map][d]
   const int t = blockIdx.x, hm = blockIdx.y, h = hm / maps, mp = hm - h * maps, kvh = h / (H / G);
@@ -123,10 +190,11 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(const TQ* _
     s_l[warp] = l;
   }
   __syncthreads();
-  float mt = -INFINITY;
+  // the sink: one more term exp(sink[h]) in the denominator, without a key or a value
+  float mt = sink != nullptr ? sink[h] : -INFINITY;
 #pragma unroll
   for (int w = 0; w < kWinWarps; ++w) mt = fmaxf(mt, s_m[w]);
-  float lt = 0.f;
+  float lt = sink != nullptr ? expf(sink[h] - mt) : 0.f;
   float f[kWinWarps];
 #pragma unroll
   for (int w = 0; w < kWinWarps; ++w) {
@@ -138,7 +206,12 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(const TQ* _
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < kWinWarps; ++w) o += sacc[w * dv + c] * f[w];
-    stf(out + (long long)t * ldo + hm * dv + c, o * inv);
+    o *= inv;
+    if (gate != nullptr) {
+      const float z = gate[(long long)t * ldg + hm * dv + c];
+      o *= gate_act == 1 ? z / (1.f + expf(-z)) : (gate_act == 2 ? 1.f / (1.f + expf(-z)) : z);
+    }
+    stf(out + (long long)t * ldo + hm * dv + c, o);
   }
 }
 
@@ -166,10 +239,11 @@ __device__ __forceinline__ void w_mma_bf16(float (&c)[4], uint32_t a0, uint32_t 
 __device__ __forceinline__ void w_cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
 }
+// tanh(x) = 1 - 2 / (exp(2x) + 1) through the hardware exponential and reciprocal: an absolute error of a few 1e-7, where the
+// one-instruction tanh.approx has a relative error of 2^-11 - too coarse for scores, which the soft cap multiplies by tens.
 __device__ __forceinline__ float tanh_approx(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
+  const float e = exp2f(fminf(x, 20.f) * 2.8853900817779268f);
+  return 1.f - __fdividef(2.f, e + 1.f);
 }
 __device__ __forceinline__ uint32_t w_pack2(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
@@ -189,6 +263,10 @@ struct WinMmaArgs {
   const int32_t* pos;
   const int32_t* slot;
   const float* bias;      // [window][H] or NULL
+  const float* sink;      // [H] or NULL: one more term exp(sink[h]) in every softmax denominator
+  const float* gate;      // [T][ldg] or NULL: the output is multiplied by act(gate) elementwise
+  long long ldg;
+  int gate_act;
   void* out;
   long long ldo;
   int max_pages, page_size, H, G, d, dv, window, maps, keep_first;
@@ -370,15 +448,35 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WinMmaArgs a) {
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  const float i0 = 1.f / l0, i1 = 1.f / l1;
-  TO* out0 = static_cast<TO*>(a.out) + (long long)(first_row + row0 / rep) * a.ldo + (h0 * a.maps + mp) * dv;
-  TO* out1 = static_cast<TO*>(a.out) + (long long)(first_row + row1 / rep) * a.ldo + (h1 * a.maps + mp) * dv;
+  float f0 = 1.f, f1 = 1.f;   // factors of the accumulators when the sink moves the reference maximum
+  if (a.sink != nullptr) {
+    const float s0 = a.sink[h0] * kLog2e, s1 = a.sink[h1] * kLog2e;
+    const float r0 = fmaxf(m0, s0), r1 = fmaxf(m1, s1);
+    f0 = exp2f(m0 - r0), f1 = exp2f(m1 - r1);
+    l0 = l0 * f0 + exp2f(s0 - r0);
+    l1 = l1 * f1 + exp2f(s1 - r1);
+  }
+  const float i0 = f0 / l0, i1 = f1 / l1;
+  const long long tr0 = first_row + row0 / rep, tr1 = first_row + row1 / rep;
+  TO* out0 = static_cast<TO*>(a.out) + tr0 * a.ldo + (h0 * a.maps + mp) * dv;
+  TO* out1 = static_cast<TO*>(a.out) + tr1 * a.ldo + (h1 * a.maps + mp) * dv;
+  const float* g0 = a.gate != nullptr ? a.gate + tr0 * a.ldg + (h0 * a.maps + mp) * dv : nullptr;
+  const float* g1 = a.gate != nullptr ? a.gate + tr1 * a.ldg + (h1 * a.maps + mp) * dv : nullptr;
+  auto gact = [&](float z) { return a.gate_act == 1 ? z / (1.f + __expf(-z)) : (a.gate_act == 2 ? 1.f / (1.f + __expf(-z)) : z); };
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     if (j < nv) {
       const int col = j * 8 + 2 * t4;
-      if (row0 < n_rows) w_st_pair(out0 + col, o[j][0] * i0, o[j][1] * i0);
-      if (row1 < n_rows) w_st_pair(out1 + col, o[j][2] * i1, o[j][3] * i1);
+      if (row0 < n_rows) {
+        float x0 = o[j][0] * i0, x1 = o[j][1] * i0;
+        if (g0 != nullptr) x0 *= gact(g0[col]), x1 *= gact(g0[col + 1]);
+        w_st_pair(out0 + col, x0, x1);
+      }
+      if (row1 < n_rows) {
+        float x0 = o[j][2] * i1, x1 = o[j][3] * i1;
+        if (g1 != nullptr) x0 *= gact(g1[col]), x1 *= gact(g1[col + 1]);
+        w_st_pair(out1 + col, x0, x1);
+      }
     }
   }
 }
@@ -681,10 +779,11 @@ extern "C" int omc_qk_norm_kv_store(const float* q, long long ldq, int nq, int q
 
 extern "C" int omc_window_attn(const void* q, long long ldq, int T, int H, int G, int d, int dv, int maps, const void* pool, int dt,
                                const int32_t* block_table, int max_pages, int page_size, const int32_t* pos, const int32_t* slot,
-                               int window, int keep_first, float scale, float softcap, const float* dist_bias, void* out, int out_dt,
-                               long long ldo, void* stream) {
+                               int window, int keep_first, float scale, float softcap, const float* dist_bias, const float* sink,
+                               const float* gate, long long ldg, int gate_act, void* out, int out_dt, long long ldo, void* stream) {
   if (q == nullptr || pool == nullptr || block_table == nullptr || pos == nullptr || slot == nullptr || out == nullptr || T < 0 ||
-      H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || maps < 1 || window < 1 || keep_first < 0 || page_size <= 0 || max_pages <= 0)
+      H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || maps < 1 || window < 1 || keep_first < 0 || page_size <= 0 || max_pages <= 0 ||
+      gate_act < 0 || gate_act > 2)
     return set_error(OMC_ERR_ARG, "omc_window_attn: bad argument");
   if (T == 0) return OMC_OK;
   if (dv > 32 * kWinMaxPerLane) return set_error(OMC_ERR_SHAPE, "omc_window_attn: value width above 256");
@@ -696,7 +795,7 @@ extern "C" int omc_window_attn(const void* q, long long ldq, int T, int H, int G
     window_attn_kernel<TC, TC, TY><<<dim3(T, H * maps), kWinWarps * 32, smem, st>>>(static_cast<const TC*>(q), ldq, H, G, d, dv, maps,
                                                                                    static_cast<const TC*>(pool), block_table, max_pages,
                                                                                    page_size, pos, slot, window, keep_first, scale, softcap,
-                                                                                   dist_bias, static_cast<TY*>(out), ldo);
+                                                                                   dist_bias, sink, gate, ldg, gate_act, static_cast<TY*>(out), ldo);
   }))
   return check_launch("omc_window_attn");
 }
@@ -710,17 +809,18 @@ extern "C" int omc_window_attn_mma_ok(int H, int G, int d, int dv) {
 extern "C" int omc_window_attn_mma(const void* q, long long ldq, int T, int H, int G, int d, int dv, int maps, const void* pool,
                                    const int32_t* block_table, int max_pages, int page_size, const int32_t* items, int n_items,
                                    const int32_t* pos, const int32_t* slot, int window, int keep_first, float scale, float softcap,
-                                   const float* dist_bias, void* out, int out_dt, long long ldo, void* stream) {
+                                   const float* dist_bias, const float* sink, const float* gate, long long ldg, int gate_act, void* out,
+                                   int out_dt, long long ldo, void* stream) {
   if (q == nullptr || pool == nullptr || block_table == nullptr || out == nullptr || T < 0 || window < 1 || maps < 1 || keep_first < 0 || page_size <= 0 ||
-      max_pages <= 0 || (items == nullptr && (pos == nullptr || slot == nullptr)) || n_items < 0)
+      gate_act < 0 || gate_act > 2 || max_pages <= 0 || (items == nullptr && (pos == nullptr || slot == nullptr)) || n_items < 0)
     return set_error(OMC_ERR_ARG, "omc_window_attn_mma: bad argument");
   if (!omc_window_attn_mma_ok(H, G, d, dv) || ldq % 8 || ldo % 2 || reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(pool) % 16)
     return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: shape or alignment not supported (see omc_window_attn_mma_ok)");
   const int n = items != nullptr ? n_items : T;
   if (n == 0) return OMC_OK;
   if ((long long)G * maps > 65535) return set_error(OMC_ERR_SHAPE, "omc_window_attn_mma: more than 65535 key/value heads");
-  WinMmaArgs a{static_cast<const bf16_t*>(q), ldq, static_cast<const bf16_t*>(pool), block_table, items, pos, slot, dist_bias, out, ldo,
-               max_pages, page_size, H, G, d, dv, window, maps, keep_first, scale, softcap, kWmRows, 0};
+  WinMmaArgs a{static_cast<const bf16_t*>(q), ldq, static_cast<const bf16_t*>(pool), block_table, items, pos, slot, dist_bias, sink, gate, ldg,
+               gate_act, out, ldo, max_pages, page_size, H, G, d, dv, window, maps, keep_first, scale, softcap, kWmRows, 0};
   if (items == nullptr) a.q_rows = ((H / G + 15) / 16) * 16;   // one token per item: only H / G rows exist, and a smaller tile lets more CTAs share an SM
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   size_t smem = sizeof(bf16_t) * ((size_t)a.q_rows * (d + 8) + 2 * (size_t)kWmKeys * (d + 8) + 2 * (size_t)kWmKeys * (dv + 8));
@@ -800,4 +900,23 @@ extern "C" int omc_diff_attn_pair(const void* q, long long ldq, int T, int H, in
   }
 #undef OMC_PAIR_LAUNCH
   return check_launch("omc_diff_attn_pair");
+}
+
+extern "C" int omc_pos_qkv_store(const float* q, long long ldq, int H, const float* k, long long ldk, int G, int d, const float* v, long long ldv,
+                                 int dv, const float* freq, int rot_dims, float temp_coef, int temp_every, int v_unit, float eps, int T,
+                                 const int32_t* pos, const int32_t* slot, const int32_t* block_table, int max_pages, int page_size, void* pool,
+                                 void* q_out, long long ldqo, int dt, void* stream) {
+  if (q == nullptr || k == nullptr || v == nullptr || pos == nullptr || slot == nullptr || block_table == nullptr || pool == nullptr ||
+      q_out == nullptr || T < 0 || H <= 0 || G <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || max_pages <= 0 ||
+      (freq != nullptr && (rot_dims < 0 || rot_dims > d || rot_dims % 2)) || (temp_coef != 0.f && temp_every <= 0))
+    return set_error(OMC_ERR_ARG, "omc_pos_qkv_store: bad argument");
+  if (T == 0) return OMC_OK;
+  const size_t smem = freq != nullptr ? sizeof(float) * (size_t)rot_dims : 0;
+  if (smem > 48 * 1024) return set_error(OMC_ERR_SHAPE, "omc_pos_qkv_store: more than 12288 rotated dimensions");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OMC_DT_SWITCH(dt, TC, {
+    pos_qkv_store_kernel<TC><<<T, 256, smem, st>>>(q, ldq, H, k, ldk, G, d, v, ldv, dv, freq, rot_dims, temp_coef, temp_every, v_unit, eps, pos,
+                                                   slot, block_table, max_pages, page_size, static_cast<TC*>(pool), static_cast<TC*>(q_out), ldqo);
+  })
+  return check_launch("omc_pos_qkv_store");
 }

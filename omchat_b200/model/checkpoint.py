@@ -21,7 +21,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from ..config import FofisunConfig, InternVisionConfig, OmChatQwen2Config, OmChatQwen2MoeConfig, TifisunConfig, VoduzenConfig
+from ..config import FofisunConfig, InternVisionConfig, OmChatQwen2Config, OmChatQwen2MoeConfig, TifisunConfig, VefunexConfig, VoduzenConfig
 
 _TEXT_KEYS = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
               "num_key_value_heads", "rms_norm_eps", "rope_theta", "max_position_embeddings")
@@ -35,8 +35,10 @@ _MOE_KEYS = ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "sha
 
 def config_from_dict(d: dict) -> OmChatQwen2Config:
     """config.json (either layout) -> OmChatQwen2Config; unknown keys are ignored, missing keys keep the defaults.
-    A config.json whose "architecture" is "Voduzen", "Tifisun" or "Fofisun" (per-layer descriptions) gives a VoduzenConfig /
-    TifisunConfig / FofisunConfig."""
+    A config.json whose "architecture" is "Voduzen", "Tifisun", "Fofisun" or "Vefunex" (per-layer descriptions) gives a
+    VoduzenConfig / TifisunConfig / FofisunConfig / VefunexConfig."""
+    if d.get("architecture") == "Vefunex" or d.get("model_type") == "vefunex":
+        return VefunexConfig.from_dict(d)
     if d.get("architecture") == "Fofisun" or d.get("model_type") == "fofisun":
         return FofisunConfig.from_dict(d)
     if d.get("architecture") == "Tifisun" or d.get("model_type") == "tifisun":

@@ -36,7 +36,8 @@ import torch
 from .. import lib, seqlib
 from ..config import ClampedMoeSpec, DiffAttentionSpec, FofisunConfig, GeluMlpSpec
 from .paged_cache import PagedStateCache
-from .seq_linear import TENSOR_GEMM_MIN_WEIGHT, dense_linear
+from .seq_linear import dense_linear
+from .seq_moe import SMALL_STEP_ROWS, expert_workspace, grouped_tensor_gemm_ok, run_sorted_experts  # noqa: F401
 from .seq_model import GraphedDecodeMixin, SequenceStepLM
 
 
@@ -197,9 +198,6 @@ def random_state_dict(cfg: FofisunConfig, seed: int = 0) -> Dict[str, torch.Tens
 
 
 # ------------------------------------------------------------------------------------------------------------------- decoder
-SMALL_STEP_ROWS = 4    # steps of up to this many rows sort their rows by expert in one single-CTA launch
-
-
 class FofisunDecoder(GraphedDecodeMixin):
     def __init__(self, cfg: FofisunConfig, w: FofisunW, dtype: torch.dtype):
         self.cfg, self.w, self.dtype = cfg, w, dtype
@@ -286,36 +284,11 @@ class FofisunDecoder(GraphedDecodeMixin):
         y = self._linear(act, lw.mlp.down, torch.float32)
         seqlib.post_norm_residual(y, lw.norm2b, self.eps, 1.0, h32, w_next, xb_out)
 
-    class _MoeWs:
-        pass
-
     def _grouped_tensor_gemm(self, s: ClampedMoeSpec) -> bool:
-        """Experts on the grouped tcgen05 GEMM (128-row tiles): bf16, tile-aligned widths, matrices large enough to matter."""
-        return (self.tensor_gemm and s.expert_ff % 128 == 0 and self.C % 128 == 0 and s.expert_ff * self.C >= TENSOR_GEMM_MIN_WEIGHT // 4)
+        return grouped_tensor_gemm_ok(self.tensor_gemm, s.expert_ff, self.C)
 
     def _moe_workspace(self, T: int, s: ClampedMoeSpec, tile: int):
-        bucket = 1 << max(T - 1, 0).bit_length()
-        key = (bucket, s.experts, s.top, s.expert_ff, tile)
-        ws = self._moe_ws.get(key)
-        if ws is None:
-            dev, i32 = self.device, torch.int32
-            ws = FofisunDecoder._MoeWs()
-            ws.max_tiles = seqlib.moe_max_tiles(bucket, s.top, s.experts, tile)
-            rows = ws.max_tiles * tile
-            ws.ids = torch.empty(bucket, s.top, device=dev, dtype=i32)
-            ws.w = torch.empty(bucket, s.top, device=dev, dtype=torch.float32)
-            ws.gate = torch.empty(bucket, device=dev, dtype=torch.float32)
-            ws.counts = torch.zeros(s.experts, device=dev, dtype=i32)
-            ws.cursor = torch.zeros(s.experts, device=dev, dtype=i32)
-            ws.seg_start = torch.zeros(s.experts + 1, device=dev, dtype=i32)
-            ws.tile_group = torch.empty(ws.max_tiles, device=dev, dtype=i32)
-            ws.slot_of = torch.empty(bucket, s.top, device=dev, dtype=i32)
-            ws.xs = torch.zeros(rows, self.C, device=dev, dtype=self.dtype)
-            ws.gu = torch.zeros(rows, 2 * s.expert_ff, device=dev, dtype=self.dtype)
-            ws.act = torch.zeros(rows, s.expert_ff, device=dev, dtype=self.dtype)
-            ws.ys = torch.empty(rows, self.C, device=dev, dtype=torch.float32)
-            self._moe_ws[key] = ws
-        return ws
+        return expert_workspace(self._moe_ws, T, s.experts, s.top, s.expert_ff, tile, self.C, self.dtype, self.device)
 
     def _moe(self, li: int, xb, h32, w_next, xb_out):
         s: ClampedMoeSpec = self.cfg.layers[li].mlp
@@ -328,23 +301,8 @@ class FofisunDecoder(GraphedDecodeMixin):
         has_gate = s.shared_ff is not None
         z32 = self._linear(xb, mw.router_cat, torch.float32)
         seqlib.router_topk(z32, s.experts, s.experts, s.top, None, has_gate, ws.ids, ws.w, ws.gate, ws.counts, bias=mw.router_bias, renorm=True)
-        max_tiles = seqlib.moe_max_tiles(T, s.top, s.experts, tile)
-        if T <= SMALL_STEP_ROWS:
-            seqlib.moe_plan_scatter_small(ws.counts, s.experts, tile, max_tiles, ws.seg_start, ws.tile_group, xb, ws.ids, s.top, ws.slot_of, ws.xs)
-        else:
-            seqlib.moe_plan_tiles(ws.counts, s.experts, tile, max_tiles, ws.seg_start, ws.cursor, ws.tile_group)
-            seqlib.moe_scatter_rows(xb, ws.ids, s.top, s.experts, ws.seg_start, ws.cursor, ws.slot_of, ws.xs)
-        rows, ff = max_tiles * tile, s.expert_ff
-        if grouped:
-            hint = min(max_tiles, T * s.top)
-            lib.gemm_grouped(ws.xs[:rows], mw.gate_up, ws.tile_group, ws.gu[:rows], lib.EPI_NONE, hint)
-        else:
-            seqlib.linear(ws.xs, mw.gate_up, ws.gu, M=rows, N=2 * ff, K=self.C, ldw=self.C, tile_group=ws.tile_group, group_stride=2 * ff * self.C)
-        seqlib.glu_mul(ws.gu[:rows], ff, seqlib.ACT_CLAMP_SWISH, ws.act[:rows], limit=s.limit, slope=cfg.SWISH_SLOPE, shift=cfg.UP_SHIFT)
-        if grouped:
-            lib.gemm_grouped(ws.act[:rows], mw.down, ws.tile_group, ws.ys[:rows], lib.EPI_NONE, hint)
-        else:
-            seqlib.linear(ws.act, mw.down, ws.ys, M=rows, N=self.C, K=ff, ldw=ff, tile_group=ws.tile_group, group_stride=self.C * ff)
+        run_sorted_experts(ws, xb, s.experts, s.top, s.expert_ff, tile, mw.gate_up, mw.down, seqlib.ACT_CLAMP_SWISH, grouped=grouped,
+                           limit=s.limit, slope=cfg.SWISH_SLOPE, shift=cfg.UP_SHIFT)
         ysh = None
         if has_gate:
             gu = self._linear(xb, mw.shared_gate_up, self.dtype)

@@ -12,10 +12,11 @@ from typing import Optional
 
 import torch
 
-from ..config import FofisunConfig, OmChatQwen2Config, OmChatQwen2MoeConfig, TifisunConfig, VoduzenConfig
+from ..config import FofisunConfig, OmChatQwen2Config, OmChatQwen2MoeConfig, TifisunConfig, VefunexConfig, VoduzenConfig
 
 # configuration class -> (module, class name)
 MODEL_CLASSES = {
+    VefunexConfig: ("omchat_b200.model.vefunex", "VefunexForCausalLM"),
     FofisunConfig: ("omchat_b200.model.fofisun", "FofisunForCausalLM"),
     TifisunConfig: ("omchat_b200.model.tifisun", "TifisunForCausalLM"),
     VoduzenConfig: ("omchat_b200.model.voduzen", "VoduzenForCausalLM"),
@@ -41,10 +42,10 @@ def read_config(path: str):
 
 def load_model(path: str, device="cuda", dtype: Optional[torch.dtype] = None):
     """The model of the checkpoint folder `path`. dtype: compute dtype for models that offer a choice (Voduzen: bfloat16 or
-    float32; Tifisun and Fofisun likewise); the OmChat models are bfloat16 only and refuse anything else."""
+    float32; Tifisun, Fofisun and Vefunex likewise); the OmChat models are bfloat16 only and refuse anything else."""
     cfg = read_config(path)
     cls = model_class_for(cfg)
-    if isinstance(cfg, (VoduzenConfig, TifisunConfig, FofisunConfig)):
+    if isinstance(cfg, (VoduzenConfig, TifisunConfig, FofisunConfig, VefunexConfig)):
         return cls.from_pretrained(path, config=cfg, device=device, dtype=dtype or torch.bfloat16)
     if dtype not in (None, torch.bfloat16):
         raise ValueError(f"{cls.__name__} computes in bfloat16 only")

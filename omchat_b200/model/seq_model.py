@@ -7,11 +7,32 @@ its weight structure in `weights_from_state_dict`.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List, Optional, Sequence
 
 import torch
 
 from .. import lib, seqlib
+
+
+def portion_starts(decoder, T: int, slot: torch.Tensor, portions: Optional[Sequence], one_row_each: bool = False):
+    """(device int32 [P + 1] with the first row of every request's portion followed by T, P): what the recurrences walk. portions:
+    the host's [(first_row, n_rows, slot, first_pos)]; without it the starts are derived from the slots (a host round trip: tests,
+    debugging). When every row is a request of its own the answer is a cached arange (`decoder._arange`)."""
+    if not one_row_each:
+        if portions is None:
+            s = slot.cpu()
+            starts = [0] + [i for i in range(1, T) if s[i] != s[i - 1]]
+        else:
+            starts = [p[0] for p in portions]
+        one_row_each = len(starts) == T
+    if one_row_each:
+        if getattr(decoder, "_arange", None) is None or decoder._arange.numel() < T + 1:
+            decoder._arange = torch.arange(max(T + 1, 65), device=decoder.device, dtype=torch.int32)
+        return decoder._arange, T
+    rb = torch.tensor(starts + [T], dtype=torch.int32)
+    if torch.device(decoder.device).type == "cuda":
+        rb = rb.pin_memory().to(decoder.device, non_blocking=True)
+    return rb, len(starts)
 
 
 class GraphedDecodeMixin:

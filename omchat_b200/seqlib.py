@@ -17,7 +17,8 @@ from .lib import OmcError, _need_cuda, _ptr, _stream
 
 _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
 DT_F32, DT_BF16 = 0, 1
-ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_GELU_ERF, ACT_CLAMP_SWISH = 0, 1, 2, 3, 4
+ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_GELU_ERF, ACT_CLAMP_SWISH, ACT_SILU = 0, 1, 2, 3, 4, 5
+ROUTER_SOFTMAX, ROUTER_SIGMOID = 0, 1
 CONV_LINEAR, CONV_SILU = 0, 1
 LINEAR_TILE = 64  # rows per tile of omc_linear's tile -> group table
 
@@ -29,15 +30,21 @@ SIGNATURES = {
     "omc_glu_mul": (_I, [_P, _I, _L, _I, _I, _I, _F, _F, _F, _P, _I, _L, _P]),
     "omc_embed_sinusoid": (_I, [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P, _L, _P]),
     "omc_diff_heads_gate": (_I, [_P, _L, _I, _I, _I, _F, _F, _F, _P, _L, _I, _P, _I, _L, _P]),
-    "omc_causal_conv": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _F, _I, _P]),
+    "omc_causal_conv": (_I, [_P, _L, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _I, _L, _I, _I, _I, _F, _I, _F, _I, _P]),
+    "omc_dyt_conv": (_I, [_P, _L, _P, _L, _F, _P, _L, _F, _P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P]),
+    "omc_dyt_rows": (_I, [_P, _L, _P, _P, _P, _I, _P, _I, _L, _I, _I, _P]),
+    "omc_tanh_cap_rows": (_I, [_P, _L, _I, _I, _F, _P]),
+    "omc_selective_scan": (_I, [_P, _I, _L, _P, _L, _P, _P, _L, _P, _L, _P, _P, _P, _L, _P, _P, _I, _L, _P, _I, _P, _P, _I, _I, _P]),
+    "omc_pos_qkv_store": (_I, [_P, _L, _I, _P, _L, _I, _I, _P, _L, _I, _P, _I, _F, _I, _I, _F, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _P]),
+    "omc_moe_combine_depth": (_I, [_P, _L, _P, _P, _I, _P, _L, _P, _L, _F, _P, _L, _F, _F, _P, _L, _L, _I, _P, _I, _P, _L, _I, _I, _P]),
     "omc_conv_qk_norm_kv_store": (_I, [_P, _L, _I, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _F, _P, _I, _I, _P, _P, _L, _I, _I, _P]),
-    "omc_linear_state_scan": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _P]),
-    "omc_map_rows": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _P]),
+    "omc_linear_state_scan": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _L, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P]),
+    "omc_map_rows": (_I, [_P, _L, _I, _I, _I, _P, _P, _I, _F, _P]),
     "omc_gated_rms_rows": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _L, _I, _P, _I, _L, _P]),
     "omc_qk_norm_kv_store": (_I, [_P, _L, _I, _I, _P, _P, _L, _I, _I, _P, _I, _P, _L, _I, _F, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _P]),
-    "omc_window_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _F, _F, _P, _P, _I, _L, _P]),
+    "omc_window_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _F, _F, _P, _P, _P, _L, _I, _P, _I, _L, _P]),
     "omc_window_attn_mma_ok": (_I, [_I, _I, _I, _I]),
-    "omc_window_attn_mma": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _I, _F, _F, _P, _P, _I, _L, _P]),
+    "omc_window_attn_mma": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _P, _I, _I, _F, _F, _P, _P, _P, _L, _I, _P, _I, _L, _P]),
     "omc_diff_attn_pair_ok": (_I, [_I, _I, _I, _I]),
     "omc_diff_attn_pair": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _I, _I, _F, _F, _F, _F, _P, _L, _I, _P, _I, _L, _P]),
     "omc_embed_scale": (_I, [_P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _I, _L, _P]),
@@ -45,14 +52,14 @@ SIGNATURES = {
     "omc_norm_residual": (_I, [_P, _L, _P, _I, _F, _P, _L, _P, _I, _L, _I, _I, _P]),
     "omc_latent_kv_store": (_I, [_P, _L, _I, _I, _I, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _I, _P]),
     "omc_latent_rope_store": (_I, [_P, _L, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _L, _I, _I, _P, _I, _P]),
-    "omc_moe_plan_scatter_small": (_I, [_P, _I, _I, _I, _P, _P, _P, _I, _L, _I, _I, _P, _I, _P, _P, _L, _P]),
+    "omc_moe_plan_scatter_small": (_I, [_P, _I, _I, _I, _P, _P, _P, _I, _L, _I, _I, _P, _I, _P, _P, _L, _P, _P]),
     "omc_rotary_q": (_I, [_P, _I, _L, _I, _I, _I, _I, _P, _I, _P, _P, _I, _I, _P]),
     "omc_latent_attn": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P, _P, _P, _F, _P, _P]),
     "omc_latent_attn_mma": (_I, [_P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _I, _P, _P, _P]),
     "omc_latent_decode_items": (_I, [_P, _P, _I, _I, _I, _P, _P, _P]),
-    "omc_router_topk": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P]),
+    "omc_router_topk": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P]),
     "omc_moe_plan_tiles": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
-    "omc_moe_scatter_rows": (_I, [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P]),
+    "omc_moe_scatter_rows": (_I, [_P, _I, _L, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P]),
     "omc_moe_combine_norm": (_I, [_P, _L, _P, _P, _I, _P, _P, _L, _P, _I, _F, _P, _L, _P, _P, _I, _L, _I, _I, _P]),
 }
 
@@ -190,13 +197,14 @@ def latent_rope_store(dkv, r: int, dr: int, w, eps: float, cs, rot_dims: int, po
     _check(rc, "omc_latent_rope_store")
 
 
-def moe_plan_scatter_small(counts, experts: int, tile: int, max_tiles: int, seg_start, tile_group, x, ids, top: int, slot_of, xs):
-    """moe_plan_tiles + moe_scatter_rows as one single-CTA launch (steps of a few rows)."""
-    _need_cuda(counts, seg_start, tile_group, x, ids, slot_of, xs)
+def moe_plan_scatter_small(counts, experts: int, tile: int, max_tiles: int, seg_start, tile_group, x, ids, top: int, slot_of, xs,
+                           row_w: Optional[torch.Tensor] = None):
+    """moe_plan_tiles + moe_scatter_rows as one single-CTA launch (steps of a few rows). row_w as in moe_scatter_rows."""
+    _need_cuda(counts, seg_start, tile_group, x, ids, slot_of, xs, row_w)
     assert x.dtype == xs.dtype
     rc = load().omc_moe_plan_scatter_small(_ptr(counts), experts, tile, max_tiles, _ptr(seg_start), _ptr(tile_group), _ptr(x), _dt(x),
                                            x.stride(0), x.shape[0], x.shape[1], _ptr(ids), top, _ptr(slot_of), _ptr(xs), xs.stride(0),
-                                           _stream())
+                                           _ptr(row_w), _stream())
     _check(rc, "omc_moe_plan_scatter_small")
 
 
@@ -326,13 +334,14 @@ def latent_attn_mma(qcat: torch.Tensor, r: int, dr: int, pool: torch.Tensor, blo
 
 def router_topk(z: torch.Tensor, e_tot: int, experts: int, top: int, correction: Optional[torch.Tensor], has_gate: bool,
                 ids: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], counts: torch.Tensor,
-                bias: Optional[torch.Tensor] = None, renorm: bool = False):
-    """bias: fp32 [e_tot] added to the logits; renorm: the weights of the chosen are divided by their sum (softmax over the chosen)."""
+                bias: Optional[torch.Tensor] = None, renorm: bool = False, score: int = ROUTER_SOFTMAX):
+    """bias: fp32 [e_tot] added to the logits; renorm: the weights of the chosen are divided by their sum (softmax over the chosen);
+    score ROUTER_SIGMOID: every output is scored by a sigmoid of its own instead of the softmax over all."""
     _need_cuda(z, correction, bias, ids, w, gate, counts)
     assert z.dtype == torch.float32 and ids.dtype == torch.int32 and w.dtype == torch.float32 and counts.dtype == torch.int32
     assert correction is None or correction.dtype == torch.float32
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == e_tot)
-    rc = load().omc_router_topk(_ptr(z), z.stride(0), z.shape[0], e_tot, experts, top, _ptr(correction), _ptr(bias), 1 if renorm else 0,
+    rc = load().omc_router_topk(_ptr(z), z.stride(0), z.shape[0], e_tot, experts, top, _ptr(correction), _ptr(bias), 1 if renorm else 0, score,
                                 1 if has_gate else 0, _ptr(ids), _ptr(w), _ptr(gate), _ptr(counts), _stream())
     _check(rc, "omc_router_topk")
 
@@ -348,12 +357,33 @@ def moe_plan_tiles(counts, experts: int, tile: int, max_tiles: int, seg_start, c
     _check(rc, "omc_moe_plan_tiles")
 
 
-def moe_scatter_rows(x, ids, top: int, experts: int, seg_start, cursor, slot_of, xs):
-    _need_cuda(x, ids, seg_start, cursor, slot_of, xs)
+def moe_scatter_rows(x, ids, top: int, experts: int, seg_start, cursor, slot_of, xs, row_w: Optional[torch.Tensor] = None):
+    """row_w fp32 [T, top]: the copy of a row for its j-th choice is multiplied by row_w[t, j] (weights on the experts' input)."""
+    _need_cuda(x, ids, seg_start, cursor, slot_of, xs, row_w)
+    assert row_w is None or (row_w.dtype == torch.float32 and row_w.is_contiguous())
     assert x.dtype == xs.dtype
     rc = load().omc_moe_scatter_rows(_ptr(x), _dt(x), x.stride(0), x.shape[0], x.shape[1], _ptr(ids), top, experts, _ptr(seg_start),
-                                     _ptr(cursor), _ptr(slot_of), _ptr(xs), xs.stride(0), _stream())
+                                     _ptr(cursor), _ptr(slot_of), _ptr(xs), xs.stride(0), _ptr(row_w), _stream())
     _check(rc, "omc_moe_scatter_rows")
+
+
+def moe_combine_depth(ys: Optional[torch.Tensor], slot_of, w: Optional[torch.Tensor], top: int, x: torch.Tensor, mult: float,
+                      streams: Optional[torch.Tensor], n_streams: int, coef: Optional[torch.Tensor], out: torch.Tensor,
+                      y1: Optional[torch.Tensor] = None, a1: float = 0.0, y2: Optional[torch.Tensor] = None, a2: float = 0.0):
+    """xn = x + a1 y1 + a2 y2 + mult * sum_j (w[t, j] | 1) ys[slot_of[t, j]] (absent terms are zero) -> streams[n_streams - 1];
+    out = sum_j coef[j] streams[j] over the first n_streams of streams fp32 [>= n_streams, T, C] (coef None: out = xn)."""
+    _need_cuda(ys, slot_of, w, x, streams, coef, out, y1, y2)
+    for t in (y1, y2):
+        assert t is None or (t.dtype == torch.float32 and t.stride(1) == 1)
+    assert x.dtype == torch.float32 and out.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1
+    assert streams is None or (streams.dtype == torch.float32 and streams.stride(2) == 1 and streams.shape[0] >= n_streams)
+    assert coef is None or (coef.is_contiguous() and coef.numel() >= n_streams)
+    rc = load().omc_moe_combine_depth(_ptr(ys), ys.stride(0) if ys is not None else 0, _ptr(slot_of), _ptr(w), top, _ptr(x), x.stride(0),
+                                      _ptr(y1), y1.stride(0) if y1 is not None else 0, a1, _ptr(y2), y2.stride(0) if y2 is not None else 0, a2,
+                                      mult, _ptr(streams), streams.stride(0) if streams is not None else 0,
+                                      streams.stride(1) if streams is not None else 0, n_streams, _ptr(coef), _dt(coef), _ptr(out),
+                                      out.stride(0), x.shape[0], x.shape[1], _stream())
+    _check(rc, "omc_moe_combine_depth")
 
 
 def moe_combine_norm(ys: Optional[torch.Tensor], slot_of, w, top: int, gate, ysh: Optional[torch.Tensor], nw, eps: float, h32, xb,
@@ -395,23 +425,24 @@ def glu_mul(z: torch.Tensor, n: int, act: int, out: torch.Tensor, limit: float =
 
 # ---- state mixers
 GATE_NONE, GATE_SILU, GATE_SIGMOID = 0, 1, 2
-DECAY_CONST, DECAY_HEAD, DECAY_CHANNEL, DECAY_GIVEN = 0, 1, 2, 3
-MAP_SILU, MAP_DECAY = 1, 2
+DECAY_CONST, DECAY_HEAD, DECAY_CHANNEL, DECAY_GIVEN, DECAY_SIGMOID_POW, DECAY_GIVEN_MINUS_ONE = 0, 1, 2, 3, 4, 5
+MAP_SILU, MAP_DECAY, MAP_SIGMOID_POW = 1, 2, 3
 
 
 def causal_conv_silu(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, state: Optional[torch.Tensor],
                      y: torch.Tensor, unit_channels: int = 0, unit_group: int = 0, unit_eps: float = 1e-6, scaled_channels: int = 0,
-                     unit_mult: float = 1.0, single_rows: bool = False, act: int = CONV_SILU):
-    """x fp32 [T, >= ch] (a column slice is fine), w [ch, taps], state fp32 [slots, taps - 1, ch] -> y fp32 [T, ch].
+                     unit_mult: float = 1.0, single_rows: bool = False, act: int = CONV_SILU, bias: Optional[torch.Tensor] = None):
+    """x fp32 [T, >= ch] (a column slice is fine), w [ch, taps], state fp32 [slots, taps - 1, ch] -> y [T, ch] (fp32 or bf16).
     single_rows: every row is a request of its own (one launch instead of two). act: CONV_SILU, or CONV_LINEAR for the weighted
-    sum itself (`causal_conv`)."""
-    _need_cuda(x, w, pos, slot, state, y)
+    sum itself (`causal_conv`). bias [ch] of w's dtype: added in front of the activation."""
+    _need_cuda(x, w, pos, slot, state, y, bias)
     ch, taps = w.shape
-    assert x.dtype == torch.float32 and y.dtype == torch.float32 and x.stride(1) == 1 and y.stride(1) == 1 and w.is_contiguous()
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and y.stride(1) == 1 and w.is_contiguous()
+    assert bias is None or (bias.dtype == w.dtype and bias.numel() == ch and bias.is_contiguous())
     assert pos.dtype == torch.int32 and slot.dtype == torch.int32
     assert taps == 1 or (state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, ch))
-    rc = load().omc_causal_conv(_ptr(x), x.stride(0), x.shape[0], ch, _ptr(w), _dt(w), taps, _ptr(pos), _ptr(slot), _ptr(state),
-                                _ptr(y), y.stride(0), act, unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
+    rc = load().omc_causal_conv(_ptr(x), x.stride(0), x.shape[0], ch, _ptr(w), _ptr(bias), _dt(w), taps, _ptr(pos), _ptr(slot), _ptr(state),
+                                _ptr(y), _dt(y), y.stride(0), act, unit_channels, unit_group, unit_eps, scaled_channels, unit_mult,
                                 1 if single_rows else 0, _stream())
     _check(rc, "omc_causal_conv")
     if taps > 1 and not single_rows:
@@ -448,9 +479,11 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: 
                       portions: int, pos: torch.Tensor, slot: torch.Tensor, H: int, G: int, dim: int, vdim: int, *, silu_in: bool = False,
                       decay_const: Optional[torch.Tensor] = None, a: Optional[torch.Tensor] = None, A_log: Optional[torch.Tensor] = None,
                       dt_bias: Optional[torch.Tensor] = None, channel_decay: bool = False, beta: Optional[torch.Tensor] = None,
-                      decay_given: bool = False):
+                      decay_given: bool = False, sigmoid_pow: Optional[float] = None, out_scale: float = 1.0):
     """The recurrence of omc_linear_state_scan; q / k / v / a / beta are fp32 2-D tensors or column slices of one.
-    decay_given: `a` [T, H * dim] already holds the per-channel decays (map_rows(..., MAP_DECAY))."""
+    decay_given: `a` [T, H * dim] already holds the per-channel decays (map_rows(..., MAP_DECAY / MAP_SIGMOID_POW)).
+    sigmoid_pow: the decay of key channel i is sigmoid(a[t, i] + dt_bias[i])^sigmoid_pow (with decay_given: `a` holds that decay
+    minus one). out_scale multiplies the read-out."""
     _need_cuda(q, k, v, state, out, row_begin, pos, slot, decay_const, a, A_log, dt_bias, beta)
     for t in (q, k, v, out, a, beta):
         assert t is None or (t.dtype == torch.float32 and t.stride(1) == 1)
@@ -458,10 +491,13 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: 
         assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dim, vdim) and row_begin.dtype == torch.int32
     mode = DECAY_CONST if decay_const is not None else (DECAY_GIVEN if decay_given else (DECAY_CHANNEL if channel_decay else DECAY_HEAD))
+    if sigmoid_pow is not None:   # given: by map_rows(..., MAP_SIGMOID_POW), which leaves the decay minus one
+        mode = DECAY_GIVEN_MINUS_ONE if decay_given else DECAY_SIGMOID_POW
     rc = load().omc_linear_state_scan(_ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), 1 if silu_in else 0, mode,
                                       _ptr(decay_const), _ptr(a), a.stride(0) if a is not None else 0, _ptr(A_log), _ptr(dt_bias),
                                       _ptr(beta), beta.stride(0) if beta is not None else 0, _ptr(state), _ptr(out), out.stride(0),
-                                      _ptr(row_begin), portions, _ptr(pos), _ptr(slot), H, G, dim, vdim, _stream())
+                                      _ptr(row_begin), portions, _ptr(pos), _ptr(slot), H, G, dim, vdim,
+                                      float(sigmoid_pow or 0.0), out_scale, _stream())
     _check(rc, "omc_linear_state_scan")
     return out
 
@@ -499,16 +535,20 @@ WINDOW_ALL = 1 << 30   # a window that never ends: plain causal attention
 
 def window_attn(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int, pos, slot,
                 window: int, scale: float, softcap: float, dist_bias: Optional[torch.Tensor], out: torch.Tensor, maps: int = 1,
-                keep_first: int = 0):
+                keep_first: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_act: int = 0):
     """q [T, H * maps * d] and pool of one dtype -> out [T, H * maps * dv]. maps: score maps per head (queries and keys of their
-    own, shared values); keep_first: the first keys of a sequence stay visible behind the window."""
-    _need_cuda(q, pool, block_table, pos, slot, dist_bias, out)
+    own, shared values); keep_first: the first keys of a sequence stay visible behind the window; sink fp32 [H]: one more
+    denominator term exp(sink[h]); gate fp32 [T, H * maps * dv] with gate_act (GATE_*): the output is multiplied by act(gate)."""
+    _need_cuda(q, pool, block_table, pos, slot, dist_bias, out, sink, gate)
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == H)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
     assert q.dtype == pool.dtype and q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
     assert pool.shape[-1] == G * (maps * d + dv)
     assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape == (window, H))
     rc = load().omc_window_attn(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, maps, _ptr(pool), _dt(pool), _ptr(block_table),
                                 block_table.shape[1], page_size, _ptr(pos), _ptr(slot), window, keep_first, scale, softcap,
-                                _ptr(dist_bias), _ptr(out), _dt(out), out.stride(0), _stream())
+                                _ptr(dist_bias), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, gate_act, _ptr(out),
+                                _dt(out), out.stride(0), _stream())
     _check(rc, "omc_window_attn")
     return out
 
@@ -533,16 +573,20 @@ def window_attn_items(portions, rep: int, device) -> torch.Tensor:
 
 def window_attn_mma(q: torch.Tensor, H: int, G: int, d: int, dv: int, pool: torch.Tensor, block_table: torch.Tensor, page_size: int,
                     items: Optional[torch.Tensor], pos, slot, window: int, scale: float, softcap: float,
-                    dist_bias: Optional[torch.Tensor], out: torch.Tensor, maps: int = 1, keep_first: int = 0):
-    """items None: every row of q is a request of its own at (slot[t], pos[t]). maps / keep_first as in window_attn."""
-    _need_cuda(q, pool, block_table, items, pos, slot, dist_bias, out)
+                    dist_bias: Optional[torch.Tensor], out: torch.Tensor, maps: int = 1, keep_first: int = 0,
+                    sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_act: int = 0):
+    """items None: every row of q is a request of its own at (slot[t], pos[t]). maps / keep_first / sink / gate as in window_attn."""
+    _need_cuda(q, pool, block_table, items, pos, slot, dist_bias, out, sink, gate)
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == H)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
     assert q.dtype == torch.bfloat16 and pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert pool.is_contiguous() and pool.shape[-1] == G * (maps * d + dv) and block_table.is_contiguous()
     assert items is None or (items.dtype == torch.int32 and items.is_contiguous() and items.shape[1] == 4)
     assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.is_contiguous() and dist_bias.shape == (window, H))
     rc = load().omc_window_attn_mma(_ptr(q), q.stride(0), q.shape[0], H, G, d, dv, maps, _ptr(pool), _ptr(block_table), block_table.shape[1],
                                     page_size, _ptr(items), items.shape[0] if items is not None else 0, _ptr(pos), _ptr(slot), window,
-                                    keep_first, scale, softcap, _ptr(dist_bias), _ptr(out), _dt(out), out.stride(0), _stream())
+                                    keep_first, scale, softcap, _ptr(dist_bias), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                    gate_act, _ptr(out), _dt(out), out.stride(0), _stream())
     _check(rc, "omc_window_attn_mma")
     return out
 
@@ -581,10 +625,95 @@ def diff_heads_gate(a: torch.Tensor, H: int, dv: int, lam: float, mult: float, e
     return out
 
 
-def map_rows(x: torch.Tensor, op: int, A_log: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, group: int = 1):
-    """In place over the fp32 rows x (a column slice is fine): MAP_SILU, or MAP_DECAY: exp(-exp(A_log[c // group]) softplus(x + bias[c]))."""
+def map_rows(x: torch.Tensor, op: int, A_log: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, group: int = 1,
+             p_exp: float = 1.0):
+    """In place over the fp32 rows x (a column slice is fine): MAP_SILU, MAP_DECAY: exp(-exp(A_log[c // group]) softplus(x + bias[c])),
+    or MAP_SIGMOID_POW: sigmoid(x + bias[c])^p_exp - 1 (the decay as its distance from 1)."""
     _need_cuda(x, A_log, bias)
     assert x.dtype == torch.float32 and x.stride(1) == 1
-    rc = load().omc_map_rows(_ptr(x), x.stride(0), x.shape[0], x.shape[1], op, _ptr(A_log), _ptr(bias), group, _stream())
+    rc = load().omc_map_rows(_ptr(x), x.stride(0), x.shape[0], x.shape[1], op, _ptr(A_log), _ptr(bias), group, p_exp, _stream())
     _check(rc, "omc_map_rows")
     return x
+
+
+# ---- tanh norm, input convolution, selective scan, positions in queries and keys
+def dyt_conv(x: torch.Tensor, alpha: torch.Tensor, nw: torch.Tensor, nb: torch.Tensor, cw: torch.Tensor, pos, slot,
+             state: Optional[torch.Tensor], u: torch.Tensor, *, y1: Optional[torch.Tensor] = None, a1: float = 0.0,
+             y2: Optional[torch.Tensor] = None, a2: float = 0.0, x_out: Optional[torch.Tensor] = None, single_rows: bool = False):
+    """With xv = x + a1 y1 + a2 y2 (written to x_out when an output is given): h = tanh(alpha xv) nw + nb, u = h + causal
+    convolution of h with cw [C, taps]; state fp32 [slots, taps - 1, C] is the ring of the last rows h of every request."""
+    _need_cuda(x, alpha, nw, nb, cw, pos, slot, state, u, y1, y2, x_out)
+    T, C = x.shape
+    taps = cw.shape[1]
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and u.stride(1) == 1 and alpha.dtype == torch.float32 and alpha.numel() == 1
+    assert nw.dtype == nb.dtype == cw.dtype and nw.numel() == C and nb.numel() == C and cw.shape[0] == C and cw.is_contiguous()
+    assert taps == 1 or (state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, C))
+    for t in (y1, y2, x_out):
+        assert t is None or (t.dtype == torch.float32 and t.stride(1) == 1)
+    rc = load().omc_dyt_conv(_ptr(x), x.stride(0), _ptr(y1), y1.stride(0) if y1 is not None else 0, a1, _ptr(y2),
+                             y2.stride(0) if y2 is not None else 0, a2, _ptr(x_out), x_out.stride(0) if x_out is not None else 0,
+                             _ptr(alpha), _ptr(nw), _ptr(nb), _ptr(cw), _dt(cw), taps, _ptr(pos), _ptr(slot), _ptr(state), _ptr(u), _dt(u),
+                             u.stride(0), T, C, 1 if single_rows else 0, _stream())
+    _check(rc, "omc_dyt_conv")
+    if taps > 1 and not single_rows:
+        _core.add_launches(1)
+    return u
+
+
+def dyt_rows(x: torch.Tensor, alpha: torch.Tensor, w: torch.Tensor, b: torch.Tensor, out: torch.Tensor):
+    """out = tanh(alpha x) w + b."""
+    _need_cuda(x, alpha, w, b, out)
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1 and w.dtype == b.dtype and alpha.dtype == torch.float32
+    rc = load().omc_dyt_rows(_ptr(x), x.stride(0), _ptr(alpha), _ptr(w), _ptr(b), _dt(w), _ptr(out), _dt(out), out.stride(0), x.shape[0],
+                             x.shape[1], _stream())
+    _check(rc, "omc_dyt_rows")
+    return out
+
+
+def tanh_cap_rows(x: torch.Tensor, cap: float):
+    """x <- cap tanh(x / cap), in place (fp32)."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.stride(1) == 1
+    rc = load().omc_tanh_cap_rows(_ptr(x), x.stride(0), x.shape[0], x.shape[1], cap, _stream())
+    _check(rc, "omc_tanh_cap_rows")
+    return x
+
+
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, B: torch.Tensor, Cm: torch.Tensor, A_log: torch.Tensor,
+                   D: torch.Tensor, z: Optional[torch.Tensor], state: torch.Tensor, out: torch.Tensor, row_begin: torch.Tensor, portions: int,
+                   pos, slot):
+    """The recurrence of omc_selective_scan: x [T, inner] (fp32 or bf16), dt / B / Cm / z fp32 rows or column slices, state fp32
+    [slots, inner, N] -> out [T, inner] = (S . C + D x) silu(z)."""
+    _need_cuda(x, dt, dt_bias, B, Cm, A_log, D, z, state, out, row_begin, pos, slot)
+    inner, N = A_log.shape
+    for t in (dt, B, Cm, z):
+        assert t is None or (t.dtype == torch.float32 and t.stride(1) == 1)
+    for t in (dt_bias, A_log, D):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (inner, N) and row_begin.dtype == torch.int32
+    assert x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] == inner and B.shape[1] == N and Cm.shape[1] == N
+    rc = load().omc_selective_scan(_ptr(x), _dt(x), x.stride(0), _ptr(dt), dt.stride(0), _ptr(dt_bias), _ptr(B), B.stride(0), _ptr(Cm),
+                                   Cm.stride(0), _ptr(A_log), _ptr(D), _ptr(z), z.stride(0) if z is not None else 0, _ptr(state), _ptr(out),
+                                   _dt(out), out.stride(0), _ptr(row_begin), portions, _ptr(pos), _ptr(slot), inner, N, _stream())
+    _check(rc, "omc_selective_scan")
+    return out
+
+
+def rotary_frequencies(dims: int, base: float, device) -> torch.Tensor:
+    """fp32 [dims / 2] on the device: f_i = base^(-2i / dims), evaluated in double precision and rounded once."""
+    return torch.tensor([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64).to(torch.float32).to(device)
+
+
+def pos_qkv_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, H: int, G: int, d: int, dv: int, pos, slot, block_table: torch.Tensor,
+                  page_size: int, pool: torch.Tensor, q_out: torch.Tensor, *, freq: Optional[torch.Tensor] = None, rot_dims: int = 0,
+                  temp_coef: float = 0.0, temp_every: int = 1, v_unit: bool = False, eps: float = 0.0):
+    """Rows of a step -> queries (rotated, with their temperature) in q_out and the cache rows [rotated k | v or unit-RMS v]."""
+    _need_cuda(q, k, v, pos, slot, block_table, pool, q_out, freq)
+    assert q.dtype == k.dtype == v.dtype == torch.float32 and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert pool.is_contiguous() and pool.shape[-1] == G * (d + dv) and pool.dtype == q_out.dtype and q_out.stride(1) == 1
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    assert freq is None or (freq.dtype == torch.float32 and freq.is_contiguous() and freq.numel() >= rot_dims // 2)
+    rc = load().omc_pos_qkv_store(_ptr(q), q.stride(0), H, _ptr(k), k.stride(0), G, d, _ptr(v), v.stride(0), dv, _ptr(freq), rot_dims,
+                                  temp_coef, temp_every, 1 if v_unit else 0, eps, q.shape[0], _ptr(pos), _ptr(slot), _ptr(block_table),
+                                  block_table.shape[1], page_size, _ptr(pool), _ptr(q_out), q_out.stride(0), _dt(pool), _stream())
+    _check(rc, "omc_pos_qkv_store")
