@@ -304,6 +304,10 @@ def main():
                     "this size (random weights; dense and mixture-of-experts feed-forwards) beside the Tifisun decoder at equal size - "
                     "prefill and decode throughput and the new kernels against their rooflines (tools/bench_fofisun.py); one JSON "
                     "line per size")
+    ap.add_argument("--vefunex", action="append", choices=["s", "m"], help="instead of the default workload: the Vefunex decoder at "
+                    "this size (random weights; attention beside a selective scan, attention, gated linear attention, experts) beside "
+                    "the Tifisun decoder at equal size - prefill and decode throughput and the new kernels against their rooflines "
+                    "(tools/bench_vefunex.py); one JSON line per size")
     ap.add_argument("--pixel-shuffle", type=float, default=1.0, help="mm_pixel_shuffle_ratio (1.0 = reference behaviour)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -331,6 +335,14 @@ def main():
         torch.cuda.set_device(0)
         for size in args.fofisun:
             print(json.dumps(measure_fofisun(size, steps=max(args.steps, 8))), flush=True)
+        return
+
+    if args.vefunex:
+        import torch
+        from tools.bench_vefunex import measure as measure_vefunex
+        torch.cuda.set_device(0)
+        for size in args.vefunex:
+            print(json.dumps(measure_vefunex(size, steps=max(args.steps, 8))), flush=True)
         return
 
     import torch

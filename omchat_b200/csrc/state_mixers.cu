@@ -463,10 +463,27 @@ __global__ void __launch_bounds__(256) gated_rms_kernel(const float* __restrict_
 // a causal convolution over time per channel whose last taps - 1 inputs h live in a ring per slot like the other convolutions'.
 // A CTA owns (1 or 8 consecutive rows + the taps - 1 rows in front of them, a block of channels): h is evaluated once per tile
 // element into shared memory, then every row's taps read the tile, a ring entry or nothing.
-template <typename TW>
-__device__ __forceinline__ float dyt_f(float x, float alpha, const TW* __restrict__ nw, const TW* __restrict__ nb, int c) {
-  return fmaf(tanhf(alpha * x), ldf(nw + c), ldf(nb + c));
+// tanh for the norm. FAST (bf16 output): 1 - 2 / (exp(2x) + 1) through the hardware exponential, absolute error of a few 1e-7 -
+// far below the rounding of the output; otherwise the library function.
+template <bool FAST>
+__device__ __forceinline__ float tanh_norm_f(float x) {
+  if (FAST) {
+    const float e = exp2f(fminf(x, 20.f) * 2.8853900817779268f);
+    return 1.f - __fdividef(2.f, e + 1.f);
+  }
+  return tanhf(x);
 }
+template <bool FAST, typename TW>
+__device__ __forceinline__ float dyt_f(float x, float alpha, const TW* __restrict__ nw, const TW* __restrict__ nb, int c) {
+  return fmaf(tanh_norm_f<FAST>(alpha * x), ldf(nw + c), ldf(nb + c));
+}
+template <typename T>
+struct is_bf16_t { static constexpr bool value = false; };
+template <>
+struct is_bf16_t<bf16_t> { static constexpr bool value = true; };
+
+constexpr int kDytRegTaps = 8;   // convolutions of up to this many taps keep a channel's weights in registers across the rows
+constexpr int kDytRows = 8;      // rows per CTA of a long step: the taps - 1 halo rows in front are evaluated once more per CTA (16 rows were slower)
 
 template <typename TW, typename TU>
 __global__ void __launch_bounds__(256) dyt_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ y1, long long ld1,
@@ -476,49 +493,84 @@ __global__ void __launch_bounds__(256) dyt_conv_kernel(const float* __restrict__
                                                        const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
                                                        float* __restrict__ state, TU* __restrict__ u, long long ldu, int T, int C, int ch_block,
                                                        int rows_per_cta, int save_here) {
+  constexpr bool FAST = is_bf16_t<TU>::value;
   extern __shared__ float tile[];  // [rows_per_cta + taps - 1][ch_block]: h of the halo rows, then of the CTA's own rows
-  __shared__ const float* src[kConvRows][kConvMaxTaps];   // where tap j of row r reads, as a pointer that takes the GLOBAL channel index
+  // where tap j of row r reads: a row of the tile (src_tile >= 0), a ring entry (src_ring != NULL, indexed by the channel), or nothing
+  __shared__ int src_tile[kDytRows][kConvMaxTaps];
+  __shared__ const float* src_ring[kDytRows][kConvMaxTaps];
   const int R = taps - 1;
   const int t0 = blockIdx.x * rows_per_cta, nr = min(rows_per_cta, T - t0);
   const int c0 = blockIdx.y * ch_block, nc = min(ch_block, C - c0);
   const float alpha = *alpha_p;
-  if (threadIdx.x < nr * taps) {
-    const int r = threadIdx.x / taps, j = threadIdx.x - r * taps;
+  for (int e = threadIdx.x; e < nr * taps; e += blockDim.x) {
+    const int r = e / taps, j = e - r * taps;
     const int t = t0 + r, p = pos[t], s = slot[t], back = R - j, sp = p - back;
+    int ti = -1;
     const float* q = nullptr;
-    if (sp >= 0) q = (back == 0 || (t - back >= 0 && slot[t - back] == s)) ? tile + (R + r - back) * ch_block - c0 : state + ((long long)s * R + sp % R) * C;
-    src[r][j] = q;
-  }
-  for (int e = threadIdx.x; e < (nr + R) * nc; e += blockDim.x) {
-    const int i = e / nc, cl = e - i * nc, c = c0 + cl, t = t0 - R + i;
-    float h = 0.f;
-    if (t >= 0) {
-      float xv = x[(long long)t * ldx + c];
-      if (y1 != nullptr) xv = fmaf(a1, y1[(long long)t * ld1 + c], xv);
-      if (y2 != nullptr) xv = fmaf(a2, y2[(long long)t * ld2 + c], xv);
-      if (i >= R && x_out != nullptr) x_out[(long long)t * ldxo + c] = xv;
-      h = dyt_f(xv, alpha, nw, nb, c);
+    if (sp >= 0) {
+      if (back == 0 || (t - back >= 0 && slot[t - back] == s)) ti = R + r - back;
+      else q = state + ((long long)s * R + sp % R) * C;
     }
-    tile[i * ch_block + cl] = h;
+    src_tile[r][j] = ti;
+    src_ring[r][j] = q;
   }
-  __syncthreads();
-  for (int e = threadIdx.x; e < nr * nc; e += blockDim.x) {
-    const int r = e / nc, cl = e - r * nc, c = c0 + cl;
-    const float h = tile[(R + r) * ch_block + cl];
-    float acc = h;
-    for (int j = 0; j < taps; ++j) {
-      const float* q = src[r][j];
-      if (q != nullptr) acc = fmaf(ldf(cw + (long long)c * taps + j), q[c], acc);
+  for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) {
+    const int c = c0 + cl;
+    const float w_n = ldf(nw + c), b_n = ldf(nb + c);
+#pragma unroll 4
+    for (int i = 0; i < nr + R; ++i) {
+      const int t = t0 - R + i;
+      float h = 0.f;
+      if (t >= 0) {
+        float xv = x[(long long)t * ldx + c];
+        if (y1 != nullptr) xv = fmaf(a1, y1[(long long)t * ld1 + c], xv);
+        if (y2 != nullptr) xv = fmaf(a2, y2[(long long)t * ld2 + c], xv);
+        if (i >= R && x_out != nullptr) x_out[(long long)t * ldxo + c] = xv;
+        h = fmaf(tanh_norm_f<FAST>(alpha * xv), w_n, b_n);
+      }
+      tile[i * ch_block + cl] = h;
     }
-    stf(u + (long long)(t0 + r) * ldu + c, acc);
-    // every row is a request of its own: nobody else reads this ring, and this thread's reads of channel c came first
-    if (save_here && R > 0) state[((long long)slot[t0 + r] * R + pos[t0 + r] % R) * C + c] = h;
+  }
+  __syncthreads();   // a thread reads its own channel only, but the pointer table came from other threads
+  for (int cl = threadIdx.x; cl < nc; cl += blockDim.x) {
+    const int c = c0 + cl;
+    float wreg[kDytRegTaps];
+    if (taps <= kDytRegTaps) {
+#pragma unroll
+      for (int j = 0; j < kDytRegTaps; ++j) wreg[j] = j < taps ? ldf(cw + (long long)c * taps + j) : 0.f;
+    }
+    for (int r = 0; r < nr; ++r) {
+      const float h = tile[(R + r) * ch_block + cl];
+      float acc = h;
+      if (taps <= kDytRegTaps) {
+#pragma unroll
+        for (int j = 0; j < kDytRegTaps; ++j) {
+          if (j < taps) {
+            const int ti = src_tile[r][j];
+            const float* q = src_ring[r][j];
+            if (ti >= 0) acc = fmaf(wreg[j], tile[ti * ch_block + cl], acc);
+            else if (q != nullptr) acc = fmaf(wreg[j], q[c], acc);
+          }
+        }
+      } else {
+        for (int j = 0; j < taps; ++j) {
+          const int ti = src_tile[r][j];
+          const float* q = src_ring[r][j];
+          const float wj = ldf(cw + (long long)c * taps + j);
+          if (ti >= 0) acc = fmaf(wj, tile[ti * ch_block + cl], acc);
+          else if (q != nullptr) acc = fmaf(wj, q[c], acc);
+        }
+      }
+      stf(u + (long long)(t0 + r) * ldu + c, acc);
+      // every row is a request of its own: nobody else reads this ring, and this thread's reads of channel c came first
+      if (save_here && R > 0) state[((long long)slot[t0 + r] * R + pos[t0 + r] % R) * C + c] = h;
+    }
   }
 }
 
 // The ring update of a step whose requests may have several rows: h of the last taps - 1 rows of every request, recomputed from the
 // (already updated) stream rows.
-template <typename TW>
+template <bool FAST, typename TW>
 __global__ void __launch_bounds__(256) dyt_state_save_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ alpha_p,
                                                              const TW* __restrict__ nw, const TW* __restrict__ nb, int C, int R, int T,
                                                              const int32_t* __restrict__ pos, const int32_t* __restrict__ slot,
@@ -528,7 +580,7 @@ __global__ void __launch_bounds__(256) dyt_state_save_kernel(const float* __rest
   if (t + R < T && slot[t + R] == s) return;
   const float alpha = *alpha_p;
   float* dst = state + ((long long)s * R + pos[t] % R) * C;
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) dst[c] = dyt_f(x[(long long)t * ldx + c], alpha, nw, nb, c);
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) dst[c] = dyt_f<FAST>(x[(long long)t * ldx + c], alpha, nw, nb, c);
 }
 
 // ---- selective scan -------------------------------------------------------------------------------------------------------
@@ -537,7 +589,7 @@ __global__ void __launch_bounds__(256) dyt_state_save_kernel(const float* __rest
 // y * silu(z). Channels are independent: a CTA owns a block of channels of one request's portion, LANES neighbouring lanes share a
 // channel (lane l holds the states l, l + LANES, ...), tokens go one after the other in chunks of kSelTok staged in shared memory.
 // A portion whose first row has position 0 starts from S = 0.
-constexpr int kSelTok = 16, kSelThreads = 128, kSelMaxPerLane = 8;
+constexpr int kSelTok = 16, kSelThreads = 128;
 
 struct SelArgs {
   const void* x;
@@ -562,7 +614,16 @@ struct SelArgs {
   int inner, N;
 };
 
-template <int LANES, typename TX, typename TY>
+// exp(x) - 1 for x <= 0 without losing the digits of a small x: a Taylor polynomial below 0.1 (truncation 1e-9 of x), the hardware
+// exponential above, where its absolute error of ~1e-7 is small against the result and such a fast decay forgets within a few tokens.
+__device__ __forceinline__ float expm1_decay_f(float x) {
+  const float p = x * fmaf(x, fmaf(x, fmaf(x, fmaf(x, 1.f / 120.f, 1.f / 24.f), 1.f / 6.f), 0.5f), 1.f);
+  const float e = exp2f(x * 1.4426950408889634f) - 1.f;
+  return x > -0.1f ? p : e;
+}
+
+// LANES neighbouring lanes share a channel; lane l holds the states l, l + LANES, ... (P of them).
+template <int LANES, int P, typename TD>
 __global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelArgs a) {
   constexpr int CH = kSelThreads / LANES;
   extern __shared__ float sm[];
@@ -578,23 +639,25 @@ __global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelArgs a) 
   if (r1 <= r0) return;
   const bool fresh = a.pos[r0] == 0;
   float* S = a.state + ((long long)a.slot[r0] * a.inner + (live ? c : 0)) * N;
-  float st[kSelMaxPerLane], A[kSelMaxPerLane];
+  float st[P], A[P];
 #pragma unroll
-  for (int r = 0; r < kSelMaxPerLane; ++r) {
+  for (int r = 0; r < P; ++r) {
     const int n = lane + r * LANES;
     const bool ok = live && n < N;
     st[r] = (ok && !fresh) ? S[n] : 0.f;
     A[r] = ok ? -expf(a.A_log[(long long)c * N + n]) : 0.f;
   }
   const float Dc = live ? a.D[c] : 0.f;
-  const TX* xg = static_cast<const TX*>(a.x);
-  TY* yg = static_cast<TY*>(a.y);
+  const TD* xg = static_cast<const TD*>(a.x);
+  TD* yg = static_cast<TD*>(a.y);
   for (int t0 = r0; t0 < r1; t0 += kSelTok) {
     const int n_tok = min(kSelTok, r1 - t0);
-    for (int e = tid; e < n_tok * ncl; e += kSelThreads) {
-      const int tt = e / ncl, j = e - tt * ncl;
-      s_dt[tt * CH + j] = softplus_f(a.dt[(long long)(t0 + tt) * a.lddt + c0 + j] + a.dt_bias[c0 + j]);
-      s_x[tt * CH + j] = ldf(xg + (long long)(t0 + tt) * a.ldx + c0 + j);
+    for (int tt = tid / CH; tt < n_tok; tt += kSelThreads / CH) {
+      const int j = tid % CH;
+      if (j < ncl) {
+        s_dt[tt * CH + j] = softplus_f(a.dt[(long long)(t0 + tt) * a.lddt + c0 + j] + a.dt_bias[c0 + j]);
+        s_x[tt * CH + j] = ldf(xg + (long long)(t0 + tt) * a.ldx + c0 + j);
+      }
     }
     for (int e = tid; e < n_tok * N; e += kSelThreads) {
       const int tt = e / N, n = e - tt * N;
@@ -608,12 +671,12 @@ __global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelArgs a) 
       const float* Ct = s_C + tt * N;
       float y = 0.f;
 #pragma unroll
-      for (int r = 0; r < kSelMaxPerLane; ++r) {
+      for (int r = 0; r < P; ++r) {
         const int n = lane + r * LANES;
         if (n < N) {
           // the decay as S + (exp(dt A) - 1) S: a decay close to 1 would lose most of the digits of 1 - decay when rounded to
           // fp32 itself, and that error grows with every token the state remembers
-          st[r] = fmaf(expm1f(dt * A[r]), st[r], st[r]) + dx * Bt[n];
+          st[r] = fmaf(expm1_decay_f(dt * A[r]), st[r], st[r]) + dx * Bt[n];
           y = fmaf(st[r], Ct[n], y);
         }
       }
@@ -622,17 +685,19 @@ __global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelArgs a) 
       if (lane == 0) s_y[tt * CH + cl] = fmaf(Dc, xv, y);
     }
     __syncthreads();
-    for (int e = tid; e < n_tok * ncl; e += kSelThreads) {
-      const int tt = e / ncl, j = e - tt * ncl;
-      float y = s_y[tt * CH + j];
-      if (a.z != nullptr) y *= silu_f(a.z[(long long)(t0 + tt) * a.ldz + c0 + j]);
-      stf(yg + (long long)(t0 + tt) * a.ldy + c0 + j, y);
+    for (int tt = tid / CH; tt < n_tok; tt += kSelThreads / CH) {
+      const int j = tid % CH;
+      if (j < ncl) {
+        float y = s_y[tt * CH + j];
+        if (a.z != nullptr) y *= silu_f(a.z[(long long)(t0 + tt) * a.ldz + c0 + j]);
+        stf(yg + (long long)(t0 + tt) * a.ldy + c0 + j, y);
+      }
     }
     // the next chunk's staging writes s_dt / s_x / s_B / s_C, which nobody reads any more; s_y is rewritten only after the next barrier
   }
   if (live) {
 #pragma unroll
-    for (int r = 0; r < kSelMaxPerLane; ++r) {
+    for (int r = 0; r < P; ++r) {
       const int n = lane + r * LANES;
       if (n < N) S[n] = st[r];
     }
@@ -792,7 +857,7 @@ extern "C" int omc_dyt_conv(const float* x, long long ldx, const float* y1, long
   const int blocks = (C + ch_block - 1) / ch_block;
   if (blocks > 65535) return set_error(OMC_ERR_SHAPE, "omc_dyt_conv: too many channel blocks");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int rows_per_cta = T >= 256 ? kConvRows : 1;
+  const int rows_per_cta = T >= 256 ? kDytRows : 1;
   const size_t smem = (size_t)ch_block * (rows_per_cta + taps - 1) * sizeof(float);
   const float* xs = (y1 != nullptr || y2 != nullptr) ? x_out : x;   // where the save kernel finds the updated stream
   const long long ldxs = (y1 != nullptr || y2 != nullptr) ? ldxo : ldx;
@@ -802,7 +867,7 @@ extern "C" int omc_dyt_conv(const float* x, long long ldx, const float* y1, long
         x, ldx, y1, ld1, a1, y2, ld2, a2, x_out, ldxo, alpha, static_cast<const TW*>(nw), static_cast<const TW*>(nb), static_cast<const TW*>(cw),
         taps, pos, slot, state, static_cast<TU*>(u), ldu, T, C, ch_block, rows_per_cta, single_rows ? 1 : 0);
     if (taps > 1 && !single_rows)
-      dyt_state_save_kernel<TW><<<dim3(T, (C + 1023) / 1024), 256, 0, st>>>(xs, ldxs, alpha, static_cast<const TW*>(nw), static_cast<const TW*>(nb), C,
+      dyt_state_save_kernel<is_bf16_t<TU>::value, TW><<<dim3(T, (C + 1023) / 1024), 256, 0, st>>>(xs, ldxs, alpha, static_cast<const TW*>(nw), static_cast<const TW*>(nb), C,
                                                                            taps - 1, T, pos, slot, state);
   }))
   return check_launch("omc_dyt_conv");
@@ -816,25 +881,33 @@ extern "C" int omc_selective_scan(const void* x, int x_dt, long long ldx, const 
       y == nullptr || row_begin == nullptr || pos == nullptr || slot == nullptr || portions < 0 || inner <= 0 || N <= 0)
     return set_error(OMC_ERR_ARG, "omc_selective_scan: bad argument");
   if (portions == 0) return OMC_OK;
-  if (N > 32 * kSelMaxPerLane) return set_error(OMC_ERR_SHAPE, "omc_selective_scan: more than 256 states per channel");
+  if (N > 256) return set_error(OMC_ERR_SHAPE, "omc_selective_scan: more than 256 states per channel");
   if (portions > 65535) return set_error(OMC_ERR_SHAPE, "omc_selective_scan: more than 65535 portions");
+  if (x_dt != y_dt) return set_error(OMC_ERR_ARG, "omc_selective_scan: x and y must have the same dtype");
   SelArgs s{x, ldx, dt, lddt, dt_bias, B, ldb, Cm, ldc, A_log, D, z, ldz, state, y, ldy, row_begin, pos, slot, inner, N};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // two states per lane up to 64 states (many short dependency chains: the loop over tokens is sequential), eight above
+  const int per = N <= 64 ? 2 : 8;
   int lanes = 1;
-  while (lanes * kSelMaxPerLane < N) lanes <<= 1;
+  while (lanes * per < N) lanes <<= 1;
   const int ch = kSelThreads / lanes;
   const size_t smem = sizeof(float) * ((size_t)3 * kSelTok * ch + 2 * (size_t)kSelTok * N);
   dim3 grid((inner + ch - 1) / ch, portions);
-#define OMC_SEL_LAUNCH(L)                                                                             \
-  OMC_DT_SWITCH(x_dt, TX, OMC_DT_SWITCH(y_dt, TY, {                                                   \
-    selective_scan_kernel<L, TX, TY><<<grid, kSelThreads, smem, st>>>(s);                             \
-  }))
-  if (lanes == 1) { OMC_SEL_LAUNCH(1) }
-  else if (lanes == 2) { OMC_SEL_LAUNCH(2) }
-  else if (lanes == 4) { OMC_SEL_LAUNCH(4) }
-  else if (lanes == 8) { OMC_SEL_LAUNCH(8) }
-  else if (lanes == 16) { OMC_SEL_LAUNCH(16) }
-  else { OMC_SEL_LAUNCH(32) }
+#define OMC_SEL_LAUNCH(L, P)                                                        \
+  OMC_DT_SWITCH(x_dt, TD, {                                                         \
+    selective_scan_kernel<L, P, TD><<<grid, kSelThreads, smem, st>>>(s);            \
+  })
+  if (per == 2) {
+    if (lanes == 1) { OMC_SEL_LAUNCH(1, 2) }
+    else if (lanes == 2) { OMC_SEL_LAUNCH(2, 2) }
+    else if (lanes == 4) { OMC_SEL_LAUNCH(4, 2) }
+    else if (lanes == 8) { OMC_SEL_LAUNCH(8, 2) }
+    else if (lanes == 16) { OMC_SEL_LAUNCH(16, 2) }
+    else { OMC_SEL_LAUNCH(32, 2) }
+  } else {
+    if (lanes == 16) { OMC_SEL_LAUNCH(16, 8) }
+    else { OMC_SEL_LAUNCH(32, 8) }
+  }
 #undef OMC_SEL_LAUNCH
   return check_launch("omc_selective_scan");
 }

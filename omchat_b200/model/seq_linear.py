@@ -22,11 +22,13 @@ _TENSOR_EPILOGUES = {seqlib.ACT_RELU2: lib.EPI_RELU2, seqlib.ACT_GELU_ERF: lib.E
 
 
 def dense_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *, tensor_gemm: bool, act: int = seqlib.ACT_NONE,
-                 alpha: float = 1.0, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """act(alpha * x @ w^T + bias) -> [rows, N] of out_dtype. x [rows, K] (fp32 or bf16, rows may be strided), w [N, K]."""
+                 alpha: float = 1.0, bias: Optional[torch.Tensor] = None, min_weight: Optional[int] = None) -> torch.Tensor:
+    """act(alpha * x @ w^T + bias) -> [rows, N] of out_dtype. x [rows, K] (fp32 or bf16, rows may be strided), w [N, K].
+    min_weight: the caller's own size threshold for the tensor-core GEMM on steps of more than 64 rows (narrow products inside a
+    mixer, which the small-matrix kernel leaves to a handful of CTAs)."""
     M, K = x.shape
     N = w.shape[0]
-    big = N * K >= (SKINNY_GEMM_MIN_WEIGHT if M <= lib.SKINNY_MAX_M else TENSOR_GEMM_MIN_WEIGHT)
+    big = N * K >= (SKINNY_GEMM_MIN_WEIGHT if M <= lib.SKINNY_MAX_M else (min_weight if min_weight is not None else TENSOR_GEMM_MIN_WEIGHT))
     if (tensor_gemm and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and big and N % 8 == 0 and K % 8 == 0
             and x.stride(0) % 8 == 0 and (act == seqlib.ACT_NONE or (act in _TENSOR_EPILOGUES and out_dtype == torch.bfloat16))):
         y = lib.gemm(x, w, bias=bias, out_f32=out_dtype == torch.float32, epi=_TENSOR_EPILOGUES.get(act, lib.EPI_NONE))

@@ -58,7 +58,8 @@ class AttentionW:
 class ScanW:
     conv: torch.Tensor             # [inner, taps]
     conv_b: torch.Tensor           # [inner]
-    x: torch.Tensor                # [dt_rank + 2 * state (+ zero rows), inner]
+    x_dt: torch.Tensor             # [dt_rank (+ zero rows), inner]: the rows of W_x that feed the step sizes
+    x_bc: torch.Tensor             # [2 * state (+ zero rows), inner]: the rows that give B and C
     dt: torch.Tensor               # [inner, dt_rank]
     dt_b: torch.Tensor             # fp32 [inner]
     A_log: torch.Tensor            # fp32 [inner, state]
@@ -74,8 +75,9 @@ class ParallelW:
 
 @dataclass
 class GlaW:
-    w_in: torch.Tensor             # [q | k | v | gate | decay factor 1 | zero rows, C]
+    w_in: torch.Tensor             # [q | k | v | gate | zero rows, C]
     cols: Dict[str, slice]
+    a1: torch.Tensor               # [rank (+ zero rows), C]: the decay's first factor, a product of its own (its output feeds a product)
     a2: torch.Tensor               # [H * dim, rank]
     a2_b: torch.Tensor             # fp32 [H * dim]
     norm: torch.Tensor             # [vdim]
@@ -160,8 +162,11 @@ def weights_from_state_dict(sd: Dict[str, torch.Tensor], cfg: VefunexConfig, dev
             mix = attention(p, m)
         elif isinstance(m, AttentionScanMixerSpec):
             r, q = m.right, p + "right."
-            wx, _ = _stack([("x", gs(q + "x", (r.dt_rank + 2 * r.state, r.inner)))], device, dtype)
-            right = ScanW(conv=gs(q + "conv", (r.inner, r.conv)), conv_b=gs(q + "conv.b", (r.inner,)), x=wx, dt=gs(q + "dt", (r.inner, r.dt_rank)),
+            wx = gs(q + "x", (r.dt_rank + 2 * r.state, r.inner))
+            x_dt, _ = _stack([("dt", wx[:r.dt_rank])], device, dtype)
+            x_bc, _ = _stack([("bc", wx[r.dt_rank:])], device, dtype)
+            right = ScanW(conv=gs(q + "conv", (r.inner, r.conv)), conv_b=gs(q + "conv.b", (r.inner,)), x_dt=x_dt, x_bc=x_bc,
+                          dt=gs(q + "dt", (r.inner, r.dt_rank)),
                           dt_b=gs(q + "dt.b", (r.inner,), f32), A_log=gs(q + "A_log", (r.inner, r.state), f32), D=gs(q + "D", (r.inner,), f32),
                           o=gs(q + "o", (C, r.inner)))
             mix = ParallelW(left=attention(p + "left.", m.left, extra=[("rin", gs(q + "in", (2 * r.inner, C)))]), right=right)
@@ -170,8 +175,9 @@ def weights_from_state_dict(sd: Dict[str, torch.Tensor], cfg: VefunexConfig, dev
             nqk, nv = m.heads * m.dim, m.heads * m.vdim
             a1 = g(p + "a1")
             w_in, cols = _stack([("q", gs(p + "q", (nqk, C))), ("k", gs(p + "k", (nqk, C))), ("v", gs(p + "v", (nv, C))),
-                                 ("g", gs(p + "g", (nv, C))), ("a1", need(a1, (a1.shape[0], C), p + "a1"))], device, dtype)
-            mix = GlaW(w_in=w_in, cols=cols, a2=gs(p + "a2", (nqk, a1.shape[0])), a2_b=gs(p + "a2.b", (nqk,), f32), norm=gs(p + "norm", (m.vdim,)),
+                                 ("g", gs(p + "g", (nv, C)))], device, dtype)
+            a1s, _ = _stack([("a1", need(a1, (a1.shape[0], C), p + "a1"))], device, dtype)
+            mix = GlaW(w_in=w_in, cols=cols, a1=a1s, a2=gs(p + "a2", (nqk, a1.shape[0])), a2_b=gs(p + "a2.b", (nqk,), f32), norm=gs(p + "norm", (m.vdim,)),
                        o=gs(p + "o", (C, nv)))
         mlp, q = None, f"l{i}.mlp."
         if spec.mlp is not None:
@@ -242,6 +248,7 @@ def random_state_dict(cfg: VefunexConfig, seed: int = 0, decay_rank: int = 16) -
 
 
 # ------------------------------------------------------------------------------------------------------------------- decoder
+NARROW_GEMM_MIN_WEIGHT = 1 << 16   # matrices of the mixers' narrow products from which the tensor-core GEMMs take them
 PREP_MIN_ROWS = 32   # average rows per request from which the decays of a recurrence are a pass of their own
 
 
@@ -293,8 +300,10 @@ class VefunexDecoder(GraphedDecodeMixin):
         return PagedStateCache(self.cache_widths(), self.state_shapes(), n_pages, n_slots, self.cfg.kv_page_size, self.dtype,
                                self.device, max_pages_per_slot)
 
-    def _linear(self, x, w, out_dtype, bias=None):
-        return dense_linear(x, w, out_dtype, tensor_gemm=self.tensor_gemm, bias=bias)
+    def _linear(self, x, w, out_dtype, bias=None, narrow: bool = False):
+        """narrow: a product with few outputs or a short K inside a mixer (low-rank factors, B | C): on long steps the tensor-core
+        GEMM takes it from a much smaller matrix on than the general rule says."""
+        return dense_linear(x, w, out_dtype, tensor_gemm=self.tensor_gemm, bias=bias, min_weight=NARROW_GEMM_MIN_WEIGHT if narrow else None)
 
     # ---- mixers: compute-dtype rows u [T, C] -> fp32 [T, C]
     def _attention(self, li: int, a: SoftmaxAttentionSpec, aw: AttentionW, z, ctx) -> torch.Tensor:
@@ -330,11 +339,13 @@ class VefunexDecoder(GraphedDecodeMixin):
         T, dev, f32, st = xz.shape[0], xz.device, torch.float32, cache.states[li]
         xc = torch.empty(T, r.inner, device=dev, dtype=self.dtype)
         seqlib.causal_conv_silu(xz[:, :r.inner], rw.conv, pos, slot, st.get("conv"), xc, single_rows=ctx["single"], bias=rw.conv_b)
-        proj = self._linear(xc, rw.x, f32)                               # [T, dt | B | C]
-        dt = self._linear(proj[:, :r.dt_rank], rw.dt, f32)               # [T, inner]; bias and softplus inside the scan
-        y = torch.empty(T, r.inner, device=dev, dtype=self.dtype)
+        # two products over xc: the low-rank step-size factor stays in the compute dtype (it feeds the next product), B | C are fp32
+        low = self._linear(xc, rw.x_dt, self.dtype, narrow=True)         # [T, dt_rank (+ pad)]
+        bc = self._linear(xc, rw.x_bc, f32, narrow=True)                 # [T, B | C (+ pad)]
+        dt = self._linear(low[:, :r.dt_rank], rw.dt, f32, narrow=True)
+        y = torch.empty(T, r.inner, device=dev, dtype=self.dtype)        # dt [T, inner]: bias and softplus inside the scan
         N = r.state
-        seqlib.selective_scan(xc, dt, rw.dt_b, proj[:, r.dt_rank:r.dt_rank + N], proj[:, r.dt_rank + N:r.dt_rank + 2 * N], rw.A_log, rw.D,
+        seqlib.selective_scan(xc, dt, rw.dt_b, bc[:, :N], bc[:, N:2 * N], rw.A_log, rw.D,
                               xz[:, r.inner:2 * r.inner], st["S"], y, ctx["row_begin"], ctx["n_portions"], pos, slot)
         return self._linear(y, rw.o, f32)
 
@@ -343,7 +354,9 @@ class VefunexDecoder(GraphedDecodeMixin):
         T, dev, f32, c = u.shape[0], u.device, torch.float32, mw.cols
         H, d, dv = m.heads, m.dim, m.vdim
         z = self._linear(u, mw.w_in, f32)
-        a = self._linear(z[:, c["a1"]], mw.a2, f32)                      # [T, H * d] decay logits (bias inside the decay function)
+        rank = mw.a2.shape[1]
+        a1 = self._linear(u, mw.a1, self.dtype, narrow=True)             # [T, rank (+ pad)]
+        a = self._linear(a1[:, :rank], mw.a2, f32, narrow=True)          # [T, H * d] decay logits (bias inside the decay function)
         o = torch.empty(T, H * dv, device=dev, dtype=f32)
         # long portions: the decays in one pass instead of in every CTA that shares a head (the same function either way)
         prep = T >= PREP_MIN_ROWS * ctx["n_portions"]

@@ -71,8 +71,8 @@ def test_weights_names_shapes_and_state_layout():
     sd = random_state_dict(cfg, seed=1)
     w = weights_from_state_dict(sd, cfg, "cpu", torch.float32)
     assert w.layers[0].mix.left.w_in.shape == (6 * 12 + 2 * 12 + 2 * 20 + 6 * 20 + 2 * 40, 72) and w.layers[0].mix.left.cols["rin"] == slice(256, 336)
-    assert w.layers[0].mix.right.x.shape == (16, 40)               # 3 + 2 * 5 rows, padded to a multiple of 8
-    assert w.layers[2].mix.w_in.shape[0] % 8 == 0 and w.layers[0].mlp.gate_up.shape == (5, 56, 72) and w.layers[1].mlp is None
+    assert w.layers[0].mix.right.x_dt.shape == (8, 40) and w.layers[0].mix.right.x_bc.shape == (16, 40)   # 3 and 2 * 5 rows, padded to multiples of 8
+    assert w.layers[2].mix.w_in.shape[0] % 8 == 0 and w.layers[2].mix.a1.shape == (16, 72) and w.layers[0].mlp.gate_up.shape == (5, 56, 72) and w.layers[1].mlp is None
     assert [l.dwa.numel() for l in w.layers] == [2, 3, 4] and w.layers[0].norm1.alpha.dtype == torch.float32
     dec = VefunexDecoder.__new__(VefunexDecoder)
     dec.cfg, dec.C = cfg, 72
